@@ -117,15 +117,16 @@ class CacheGroup:
         self.n_pages = n_pages
         self.pool = None                      # a PoolView, set by the manager once the books exist
         shape = (n_pages, req.kv_heads, page_size, req.head_dim)
+        v_shape = (n_pages, req.kv_heads, page_size, req.value_dim)      # values may be narrower or wider than keys
         # Zeroed once (the reference leaves its pools uninitialised, scratch.rs:546-573).  A key is always
         # written before any query can see it, but the tensor-core attention fetches whole pages, masked slots
         # included, and a masked probability of 0 times a stray NaN would still be NaN.
         self.k = {c: torch.zeros(shape, dtype=dtype, device=device) for c in owners}
-        self.v = {c: torch.zeros(shape, dtype=dtype, device=device) for c in owners}
+        self.v = {c: torch.zeros(v_shape, dtype=dtype, device=device) for c in owners}
 
     def bytes_per_token(self) -> int:
         any_pool = next(iter(self.k.values()))
-        return 2 * len(self.owners) * self.req.kv_heads * self.req.head_dim * any_pool.element_size()
+        return len(self.owners) * self.req.kv_heads * (self.req.head_dim + self.req.value_dim) * any_pool.element_size()
 
 
 @dataclass
@@ -164,7 +165,8 @@ class CacheManager:
                 src = plans[plan.cache_from]
                 if src.kv is None or src.cache_from is not None:
                     raise ValueError(f"call {ci} reads the cache of call {plan.cache_from}, which owns none")
-                if plan.kv is not None and (plan.kv.kv_heads, plan.kv.head_dim) != (src.kv.kv_heads, src.kv.head_dim):
+                if plan.kv is not None and (plan.kv.kv_heads, plan.kv.head_dim, plan.kv.value_dim) != \
+                        (src.kv.kv_heads, src.kv.head_dim, src.kv.value_dim):
                     raise ValueError(f"call {ci} and call {plan.cache_from} disagree on the cache geometry")
                 # pages are given back by the owner's window: a reader that looks further back than the owner
                 # would ask for keys whose pages are gone

@@ -91,10 +91,26 @@ class ConfigReader:
         return v
 
     def architecture(self) -> str:
+        """The architecture's name: `architectures[0]`, or the string under `architecture` in files that name
+        one architecture only."""
         archs = self.raw.get("architectures")
-        if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-            raise MissingKey("architectures")
-        return archs[0]
+        if isinstance(archs, list) and archs and isinstance(archs[0], str):
+            return archs[0]
+        one = self.raw.get("architecture")
+        if isinstance(one, str) and one:
+            return one
+        raise MissingKey("architectures")
+
+    def section(self, key, default=_MISSING, where: str = "config.json") -> "ConfigReader":
+        """A nested object as a reader of its own (None where it is absent or null and a default is given)."""
+        v = self.raw.get(key, _MISSING)
+        if v is _MISSING or v is None:
+            if default is _MISSING:
+                raise MissingKey(key, where)
+            return default
+        if not isinstance(v, dict):
+            raise BadValue(key, v, "must be an object")
+        return ConfigReader(v)
 
 
 def read_config_json(folder_or_file) -> dict:

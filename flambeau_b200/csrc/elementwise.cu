@@ -5,11 +5,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------
-// Embedding: x[t,:] = E[ids[t],:]  (crates/forward/src/core/composites/embed.rs:26-62)
+// Embedding: x[t,:] = E[ids[t],:] * scale  (crates/forward/src/core/composites/embed.rs:26-62; scale 1 there)
 // ---------------------------------------------------------------------------
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ x, int H, int V, int* status) {
+                                 float* __restrict__ x, int H, int V, float scale, int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int t = blockIdx.x;
@@ -20,16 +20,16 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
     }
     const TT* src = table + (size_t)id * H;
     float* dst = x + (size_t)t * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = fb_to_float(src[c]);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = fb_to_float(src[c]) * scale;
 }
 
 FB_API int fb_embedding(const void* table, int table_dtype, const int* ids, float* x, int n, int H,
-                        int V, int* status, cudaStream_t stream) {
+                        int V, float scale, int* status, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && H > 0 && V > 0, "embedding: bad sizes n=%d H=%d V=%d", n, H, V);
     if (n == 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     FB_DISPATCH_DTYPE(table_dtype, TT,
-        fb_launch((embedding_kernel<TT>), n, threads, 0, stream, (const TT*)table, ids, x, H, V, status));
+        fb_launch((embedding_kernel<TT>), n, threads, 0, stream, (const TT*)table, ids, x, H, V, scale, status));
     return fb_check_launch("embedding");
 }
 
@@ -295,6 +295,109 @@ FB_API int fb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_pa
         return (launch_add_rmsnorm<TD, TW, TO>(x, delta, n_partials, (size_t)partial_stride, w, out, rows,
                                                n_out, H, eps, w_offset, stream)))));
     return 0;
+}
+
+// ---------------------------------------------------------------------------
+// A part's output that is normalised before it joins the stream (blocks with a norm after each sublayer as well
+// as before it), fused with the norm that follows:
+//   r = rows ? rows[j] : j
+//   d = sum_p delta[p][r]                                   (float32 slabs, split-K shares of the part's last product)
+//   v = x[r] + d * (wd + wd_offset) / sqrt(mean(d^2) + eps_d)
+//   if (!rows) x[r] = v                                      (the stream is updated in place)
+//   if (out)   out[j] = v * (w + w_offset) / sqrt(mean(v^2) + eps)
+// Both sums of squares and all products are float32.  Each thread keeps its VPT elements of the row in registers.
+// ---------------------------------------------------------------------------
+template <typename TWD, typename TW, typename TO, int VPT>
+__global__ void __launch_bounds__(1024)
+norm_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_partials, size_t partial_stride,
+                        const TWD* __restrict__ wd, float eps_d, float wd_offset, const TW* __restrict__ w,
+                        TO* __restrict__ out, const int* __restrict__ rows, int H, float eps, float w_offset) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    __shared__ float red[32];
+    const int j = blockIdx.x;
+    const int r = rows ? rows[j] : j;
+    float* xr = x + (size_t)r * H;
+    float d[VPT], v[VPT];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        d[i] = 0.0f;
+        v[i] = c < H ? xr[c] : 0.0f;
+        if (c < H)
+            for (int p = 0; p < n_partials; ++p) d[i] += delta[(size_t)p * partial_stride + (size_t)r * H + c];
+        ss += d[i] * d[i];
+    }
+    ss = fb_block_sum(ss, red);
+    const float inv_d = 1.0f / sqrtf(ss / (float)H + eps_d);
+    ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < H) {
+            v[i] += d[i] * inv_d * (fb_to_float(wd[c]) + wd_offset);
+            if (!rows) xr[c] = v[i];
+        }
+        ss += v[i] * v[i];
+    }
+    if (!out) return;
+    ss = fb_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)j * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < H) o[c] = fb_from_float<TO>(v[i] * (fb_to_float(w[c]) + w_offset) * inv);
+    }
+}
+
+FB_API int fb_norm_add_rmsnorm(float* x, const float* delta, int n_partials, long long partial_stride,
+                               const void* wd, int wd_dtype, float eps_d, float wd_offset, const void* w, int w_dtype,
+                               void* out, int out_dtype, const int* rows, int n_out, int H, float eps, float w_offset,
+                               cudaStream_t stream) {
+    FB_REQUIRE(n_out >= 0 && H > 0 && H <= 16384, "norm_add_rmsnorm: bad sizes n=%d H=%d", n_out, H);
+    FB_REQUIRE(delta && wd && n_partials >= 1, "norm_add_rmsnorm: nothing to add");
+    FB_REQUIRE(eps > 0.0f && eps_d > 0.0f, "norm_add_rmsnorm: eps must be positive");
+    FB_REQUIRE(!out || w, "norm_add_rmsnorm: an output needs its weight");
+    if (n_out == 0) return 0;
+    if (!out) { w = wd; w_dtype = wd_dtype; out_dtype = FB_F32; }
+    const int threads = H >= 4096 ? 1024 : H >= 1024 ? 512 : H >= 256 ? 256 : 128;   // H / threads <= 16
+    const int vpt = (H + threads - 1) / threads;
+#define FB_NAN_CASE(V)                                                                                             \
+    FB_DISPATCH_DTYPE(wd_dtype, TWD, FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,               \
+        (fb_launch((norm_add_rmsnorm_kernel<TWD, TW, TO, V>), n_out, threads, 0, stream, x, delta, n_partials,     \
+                   (size_t)partial_stride, (const TWD*)wd, eps_d, wd_offset, (const TW*)w, (TO*)out, rows, H, eps,  \
+                   w_offset)))))
+    if (vpt <= 1) FB_NAN_CASE(1); else if (vpt <= 2) FB_NAN_CASE(2); else if (vpt <= 4) FB_NAN_CASE(4);
+    else if (vpt <= 8) FB_NAN_CASE(8); else FB_NAN_CASE(16);
+#undef FB_NAN_CASE
+    return fb_check_launch("norm_add_rmsnorm");
+}
+
+// ---------------------------------------------------------------------------
+// out[t] = [a[t] ; b[t]] in the output's type: two float32 streams of one width side by side, as the input of a
+// linear map that mixes them (a model that feeds its embedding into later layers again).
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out,
+                                   int n, int H) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * 2 * H) return;
+    const int t = (int)(idx / (2 * H)), c = (int)(idx - (size_t)t * 2 * H);
+    out[idx] = fb_from_float<TO>(c < H ? a[(size_t)t * H + c] : b[(size_t)t * H + c - H]);
+}
+
+FB_API int fb_concat_cast(const float* a, const float* b, void* out, int out_dtype, int n, int H,
+                          cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && H > 0 && a && b && out, "concat_cast: bad arguments");
+    if (n == 0) return 0;
+    const size_t total = (size_t)n * 2 * H;
+    FB_DISPATCH_DTYPE(out_dtype, TO,
+        (fb_launch((concat_cast_kernel<TO>), (unsigned)((total + 255) / 256), 256, 0, stream, a, b, (TO*)out, n, H)));
+    return fb_check_launch("concat_cast");
 }
 
 // ---------------------------------------------------------------------------

@@ -26,7 +26,9 @@ _SIGNATURES = {
     "fb_set_attention_tc": (None, [I]),
     "fb_set_gemm_pair": (None, [I]),
     # elementwise.cu
-    "fb_embedding": (I, [P, I, P, P, I, I, I, P, STREAM]),
+    "fb_embedding": (I, [P, I, P, P, I, I, I, F, P, STREAM]),
+    "fb_norm_add_rmsnorm": (I, [P, P, I, L, P, I, F, F, P, I, P, I, P, I, I, F, F, STREAM]),
+    "fb_concat_cast": (I, [P, P, P, I, I, I, STREAM]),
     "fb_add_rmsnorm": (I, [P, P, I, I, L, P, I, P, I, P, I, I, F, F, STREAM]),
     "fb_rope_table": (I, [P, P, P, P, I, I, STREAM]),
     "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P, STREAM]),
@@ -39,6 +41,11 @@ _SIGNATURES = {
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
     "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, F, P, P, STREAM]),
+    # diff_attention.cu
+    "fb_qkv_bias_cache_write": (I, [P, L, I, L, P, I, P, L, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, P,
+                                    STREAM]),
+    "fb_diff_attention_simt": (I, [P, L, P, L, I, P, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, F, F, F, F, P,
+                                   STREAM]),
     # attention_mma.cu
     "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P, L, P, L,
                                    L, I, P, STREAM]),

@@ -62,7 +62,9 @@ def _i32(t, what):
 
 # ---------------------------------------------------------------------------
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
+def embedding(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, status: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """x[t] = table[ids[t]] * scale, float32."""
     _cuda(table, ids, x, status)
     _i32(ids, "token ids")
     V, H = table.shape
@@ -71,7 +73,7 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, status: t
             or not table.is_contiguous():
         raise KernelError("embedding: the stream must be contiguous float32 [n, width]")
     check(lib().fb_embedding(table.data_ptr(), dtype_code(table), ids.data_ptr(), x.data_ptr(), n, H, V,
-                             status.data_ptr(), _stream()), "embedding")
+                             float(scale), status.data_ptr(), _stream()), "embedding")
 
 
 def add_rms_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -99,6 +101,99 @@ def add_rms_norm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: 
                                n_partials, stride, weight.data_ptr(), dtype_code(weight), out.data_ptr(),
                                dtype_code(out), _ptr(rows), n_out, H, float(eps), float(weight_offset), _stream()),
           "add_rms_norm")
+
+
+def norm_add_rms_norm(x: torch.Tensor, delta: torch.Tensor, delta_weight: torch.Tensor, delta_eps: float,
+                      delta_weight_offset: float, weight, eps: float, out, rows=None, n_partials: int = 1,
+                      n_rows: int | None = None, partial_stride: int = 0, weight_offset: float = 0.0) -> None:
+    """x[r] += rmsnorm(sum_p delta_p[r]) * (delta_weight + delta_weight_offset) (written back to x without `rows`),
+    then out[j] = rmsnorm(x[r]) * (weight + weight_offset), r = rows[j] or j.  `out` (and `weight`) may be None:
+    only the stream is updated.  delta is float32 [n, H], with n_partials > 1 the first of that many slabs
+    `partial_stride` elements apart."""
+    _cuda(x, delta, delta_weight, weight, out, rows)
+    _i32(rows, "rows")
+    H = x.shape[1]
+    n_out = rows.numel() if rows is not None else (x.shape[0] if n_rows is None else n_rows)
+    if x.dtype != torch.float32 or not x.is_contiguous() or delta.dtype != torch.float32 or not delta.is_contiguous() \
+            or delta.shape[-1] != H or delta_weight.numel() != H:
+        raise KernelError("norm_add_rms_norm: the stream and the delta must be contiguous float32 of one width")
+    if out is not None and (not out.is_contiguous() or out.shape[-1] != H or out.shape[0] < n_out
+                            or weight is None or weight.numel() != H):
+        raise KernelError("norm_add_rms_norm: bad output")
+    if out is None and rows is not None:
+        raise KernelError("norm_add_rms_norm: nothing to do (no output, and chosen rows are not written back)")
+    stride = int(partial_stride) if n_partials > 1 else 0
+    if n_partials > 1 and stride <= 0:
+        raise KernelError("norm_add_rms_norm: several slabs need their stride")
+    check(lib().fb_norm_add_rmsnorm(x.data_ptr(), delta.data_ptr(), int(n_partials), stride, delta_weight.data_ptr(),
+                                    dtype_code(delta_weight), float(delta_eps), float(delta_weight_offset),
+                                    _ptr(weight), dtype_code(weight) if weight is not None else 0, _ptr(out),
+                                    dtype_code(out) if out is not None else 0, _ptr(rows), n_out, H, float(eps),
+                                    float(weight_offset), _stream()), "norm_add_rms_norm")
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] ; b[t]] in out's dtype; a and b are contiguous float32 [n, H]."""
+    _cuda(a, b, out)
+    n, H = a.shape
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or tuple(b.shape) != (n, H) or not a.is_contiguous() \
+            or not b.is_contiguous() or tuple(out.shape) != (n, 2 * H) or not out.is_contiguous():
+        raise KernelError("concat_cast: two contiguous float32 [n, H] in, one contiguous [n, 2H] out")
+    check(lib().fb_concat_cast(a.data_ptr(), b.data_ptr(), out.data_ptr(), dtype_code(out), n, H, _stream()),
+          "concat_cast")
+
+
+def qkv_bias_cache_write(proj: torch.Tensor, bias, q_out: torch.Tensor, gate_out, cache, positions, row_seq,
+                         nh: int, nkv: int, qd: int, vd: int, n_gate: int, status, n_partials: int = 1,
+                         partial_stride: int = 0) -> None:
+    """What follows a fused projection whose float32 rows hold [q: nh*qd | k: nkv*qd | v: nkv*vd | gate: n_gate],
+    possibly as split-K shares: the shares are added, `bias` (over the q, k and v columns, optional) is added,
+    q goes to q_out, k and v into their pages (pools [pages, nkv, page size, qd] and [.., vd]) when the cache view
+    is writable, and gate_out (float32 [n, n_gate]) = sigmoid of the gate columns."""
+    _cuda(proj, bias, q_out, gate_out, positions, row_seq, status)
+    n = proj.shape[0]
+    if proj.dtype != torch.float32 or q_out.shape[0] != n or q_out.shape[1] != nh * qd:
+        raise KernelError("qkv_bias_cache_write: float32 projection rows and q [n, heads * size] wanted")
+    if bias is not None and (bias.numel() != nh * qd + nkv * qd + nkv * vd or not bias.is_contiguous()):
+        raise KernelError("qkv_bias_cache_write: the bias covers the q, k and v columns")
+    if n_gate and (gate_out is None or gate_out.dtype != torch.float32 or not gate_out.is_contiguous()
+                   or tuple(gate_out.shape) != (n, n_gate)):
+        raise KernelError("qkv_bias_cache_write: the gate wants contiguous float32 [n, gates]")
+    k_pool, v_pool = cache.k_pool, cache.v_pool
+    n_pages = k_pool.shape[0]
+    if tuple(k_pool.shape) != (n_pages, nkv, cache.page_size, qd) or tuple(v_pool.shape) != (n_pages, nkv, cache.page_size, vd) \
+            or not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.dtype != q_out.dtype \
+            or v_pool.dtype != q_out.dtype:
+        raise KernelError("qkv_bias_cache_write: pools must be contiguous [pages, kv heads, page size, size] in q's dtype")
+    check(lib().fb_qkv_bias_cache_write(
+        proj.data_ptr(), _rows(proj), int(n_partials), int(partial_stride), _ptr(bias),
+        dtype_code(bias) if bias is not None else 0, q_out.data_ptr(), _rows(q_out), dtype_code(q_out),
+        _ptr(gate_out), positions.data_ptr(), row_seq.data_ptr(), cache.block_table.data_ptr(),
+        cache.block_table.stride(0), _ptr(cache.table_base), k_pool.data_ptr(), v_pool.data_ptr(), cache.page_size,
+        n_pages, n, nh, nkv, qd, vd, n_gate, 1 if cache.writable else 0, status.data_ptr(), _stream()),
+        "qkv_bias_cache_write")
+
+
+def diff_attention_simt(q, out, gate, cache, positions, row_seq, nh: int, nkv: int, kd: int, vd: int, window: int,
+                        scale: float, lam: float, eps: float, out_scale: float, status) -> None:
+    """Differential attention with float32 math on the CUDA cores (see csrc/diff_attention.cu): q [n, nh*2*kd],
+    out [n, nh*vd], gate float32 [n, nh] or None."""
+    _cuda(q, out, gate, positions, row_seq, status)
+    n = q.shape[0]
+    k_pool, v_pool = cache.k_pool, cache.v_pool
+    n_pages = k_pool.shape[0]
+    if q.shape[1] != nh * 2 * kd or tuple(out.shape) != (n, nh * vd) or tuple(k_pool.shape[1:]) != (nkv, cache.page_size, 2 * kd) \
+            or tuple(v_pool.shape[1:]) != (nkv, cache.page_size, vd):
+        raise KernelError("diff attention: shapes do not match the head counts")
+    if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype):
+        raise KernelError("diff attention: q, out and the cache must share one dtype")
+    if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (n, nh) or not gate.is_contiguous()):
+        raise KernelError("diff attention: the gate wants contiguous float32 [n, heads]")
+    check(lib().fb_diff_attention_simt(
+        q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), dtype_code(q), _ptr(gate), k_pool.data_ptr(),
+        v_pool.data_ptr(), cache.page_size, n_pages, cache.block_table.data_ptr(), cache.block_table.stride(0),
+        _ptr(cache.table_base), positions.data_ptr(), row_seq.data_ptr(), n, nh, nkv, kd, vd, int(window),
+        float(scale), float(lam), float(eps), float(out_scale), status.data_ptr(), _stream()), "diff_attention_simt")
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
@@ -461,3 +556,13 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
                              nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
                              score_slopes=score_slopes)
+
+
+def diff_attention(ctx, q, out, gate, cache, nh: int, nkv: int, kd: int, vd: int, window: int, scale: float,
+                   lam: float, eps: float, out_scale: float) -> None:
+    """Differential attention of every row of the step over its request's cached keys and values, with the kernel
+    that fits the dtype and the sizes: the float32-math kernel for the 32-bit mode and for sizes the tensor-core
+    arrangements do not take."""
+    b = ctx.batch
+    diff_attention_simt(q, out, gate, cache, b.positions, b.row_seq, nh, nkv, kd, vd, window, scale, lam, eps,
+                        out_scale, ctx.runtime.status)

@@ -26,10 +26,11 @@ class DecoderModel:
         self.order = list(spec.order)
         self.final_norm = build_part(spec.final_norm, runtime)
         self.head = build_part(spec.head, runtime)
+        self.reentry = build_part(spec.reentry, runtime) if spec.reentry is not None else None
 
     # ---- weights -----------------------------------------------------------
     def parts(self):
-        return [self.embedding, *self.layers, self.final_norm, self.head]
+        return [p for p in (self.embedding, self.reentry, *self.layers, self.final_norm, self.head) if p is not None]
 
     def tensor_specs(self) -> dict:
         specs = {}
@@ -52,6 +53,8 @@ class DecoderModel:
         total = self.final_norm.weight_bytes() + self.head.weight_bytes()
         for call in self.order:
             total += self.layers[call.layer].weight_bytes()
+            if call.reenter:
+                total += self.reentry.weight_bytes()
         return total
 
     # ---- what the cache manager must provide ---------------------------------
@@ -71,13 +74,21 @@ class DecoderModel:
         x = ctx.open_stream(self.hidden_size)
         self.embedding.forward(ctx, b.token_ids[:n], x)
         stream = ResidualStream(x)
+        x0 = None
+        if self.reentry is not None:
+            # the embedding output is wanted again later: the layers work on a copy of it (one device-to-device copy)
+            x0 = x
+            stream.x = ctx.step_alloc((n, self.hidden_size), torch.float32)
+            stream.x.copy_(x0)
         for ci, call in enumerate(self.order):
+            if call.reenter:
+                self.reentry.forward(ctx, stream, x0)
             self.layers[call.layer].forward(ctx, stream, ci)
         if b.n_out == 0:
             return None
         h = ctx.step_alloc((b.n_out, self.hidden_size), rt.dtype)
         self.final_norm.add_norm(ctx, stream.x, stream.pending, h, rows=b.out_rows[:b.n_out],
-                                 n_partials=stream.pending_slabs)
+                                 n_partials=stream.pending_slabs, delta_norm=stream.pending_norm)
         logits = ctx.logits(b.n_out, self.vocab_size)
         self.head.forward(ctx, h, logits)
         return logits

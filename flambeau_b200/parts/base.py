@@ -9,9 +9,11 @@ never which model it sits in.  Every part
 
 Categories and the method each must have:
 
-  norm           add_norm(ctx, x, delta, out, rows=None, n_partials=1)
+  norm           add_norm(ctx, x, delta, out, rows=None, n_partials=1, delta_norm=None)
                  x: float32 stream [n, width], updated in place with delta when
-                 rows is None; out: normalised rows in the engine dtype.
+                 rows is None; out: normalised rows in the engine dtype (None:
+                 only the stream is updated).  delta_norm: a norm that the
+                 delta passes through before it is added.
                  normalize(ctx, x, out): the norm of every row of x alone.
   position       prepare(ctx) -> per-step tables (memoised in ctx.shared);
                  rotate(ctx, q, k) in place on [n, heads*head_dim] views.
@@ -38,8 +40,13 @@ class KVRequirement:
     """A mixer that keeps keys and values: layers with equal requirements share
     a cache group (one page-id space, one block table per request)."""
     kv_heads: int
-    head_dim: int
+    head_dim: int            # elements of a key row (per key/value head)
     window: int = 0          # 0 = all earlier keys stay live; W > 0 = only the last W
+    v_head_dim: int = 0      # elements of a value row where it differs from a key row (0: the same)
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -119,7 +126,7 @@ class FeedForward(Part):
 class Norm(Part):
     category = "norm"
 
-    def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1) -> None:
+    def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1, delta_norm=None) -> None:
         raise NotImplementedError
 
     def normalize(self, ctx, x, out) -> None:

@@ -8,26 +8,29 @@ from .spec import register_part
 
 
 class TokenEmbedding(Part):
-    """x[t,:] = E[token[t],:], no scale (crates/forward/src/core/composites/embed.rs:26-62)."""
+    """x[t,:] = E[token[t],:] * scale in float32; scale 1 in the plain case
+    (crates/forward/src/core/composites/embed.rs:26-62).  The tensor is `<prefix><weight_name>`."""
     graph_safe = True
     category = "embedding"
 
-    def __init__(self, runtime=None, prefix="", *, vocab: int, width: int, init_std: float = 0.02):
+    def __init__(self, runtime=None, prefix="", *, vocab: int, width: int, init_std: float = 0.02,
+                 scale: float = 1.0, weight_name: str = "weight"):
         super().__init__(runtime, prefix)
         self.vocab, self.width, self.init_std = int(vocab), int(width), init_std
+        self.scale, self.weight_name = float(scale), weight_name
         self.table = None
 
     def own_tensor_specs(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab, self.width), init=("normal", self.init_std))}
+        return {self.prefix + self.weight_name: TensorSpec((self.vocab, self.width), init=("normal", self.init_std))}
 
     def own_bind(self, tensors):
-        self.table = tensors[self.prefix + "weight"]
+        self.table = tensors[self.prefix + self.weight_name]
 
     def own_weights(self):
         return []          # a step reads n rows of the table, not the table
 
     def forward(self, ctx, token_ids, x):
-        ops.embedding(self.table, token_ids, x, self.runtime.status)
+        ops.embedding(self.table, token_ids, x, self.runtime.status, self.scale)
 
 
 class LMHead(Part):
@@ -38,17 +41,18 @@ class LMHead(Part):
     category = "head"
 
     def __init__(self, runtime=None, prefix="", *, vocab: int, width: int, tied_to: str | None = None,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, weight_name: str = "weight"):
         super().__init__(runtime, prefix)
         self.vocab, self.width, self.tied_to, self.init_std = int(vocab), int(width), tied_to, init_std
+        self.weight_name = weight_name
         self.proj = None
 
     def own_tensor_specs(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab, self.width), init=("normal", self.init_std),
-                                                   alias_of=self.tied_to)}
+        return {self.prefix + self.weight_name: TensorSpec((self.vocab, self.width), init=("normal", self.init_std),
+                                                           alias_of=self.tied_to)}
 
     def own_bind(self, tensors):
-        self.proj = Linear(tensors[self.prefix + "weight"])
+        self.proj = Linear(tensors[self.prefix + self.weight_name])
 
     def own_weights(self):
         return [self.proj.weight]

@@ -20,9 +20,14 @@ class GatedMLP(FeedForward):
     activations (kernels.ops.ACTIVATIONS)."""
     graph_safe = True
 
+    DEFAULT_NAMES = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
     def __init__(self, runtime=None, prefix="", *, width: int, inner: int, activation: str = "silu",
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, names=DEFAULT_NAMES):
         super().__init__(runtime, prefix)
+        self.names = tuple(names)                # what the gate, up and down tensors are called behind the prefix
+        if len(self.names) != 3:
+            raise ValueError("gated feed-forward: three tensor names wanted (gate, up, down)")
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"gated feed-forward: activation '{activation}' is not implemented "
                              f"({', '.join(sorted(ops.ACTIVATIONS))})")
@@ -32,16 +37,18 @@ class GatedMLP(FeedForward):
 
     def own_tensor_specs(self):
         p, init = self.prefix, ("normal", self.init_std)
+        gate, up, down = self.names
         return {
-            p + "gate_proj.weight": TensorSpec((self.inner, self.width), init=init),
-            p + "up_proj.weight": TensorSpec((self.inner, self.width), init=init),
-            p + "down_proj.weight": TensorSpec((self.width, self.inner), init=init),
+            p + gate: TensorSpec((self.inner, self.width), init=init),
+            p + up: TensorSpec((self.inner, self.width), init=init),
+            p + down: TensorSpec((self.width, self.inner), init=init),
         }
 
     def own_bind(self, tensors):
         p = self.prefix
-        self.gate_up = Linear(interleave_rows(tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]))
-        self.down = Linear(tensors[p + "down_proj.weight"])
+        gate, up, down = self.names
+        self.gate_up = Linear(interleave_rows(tensors[p + gate], tensors[p + up]))
+        self.down = Linear(tensors[p + down])
         # Few rows (decoding): when the stacked matrix has at least as many 128-row tiles as the device has SMs,
         # one CTA per tile streams its rows over the whole of K and applies the activation in its epilogue; that
         # many CTAs draw the full memory bandwidth, and the separate activation kernel and the float32 shares it

@@ -15,25 +15,36 @@ class RMSNorm(Norm):
     graph_safe = True
 
     def __init__(self, runtime=None, prefix="", *, width: int, eps: float, init=("one_plus_normal", 0.02),
-                 weight_offset: float = 0.0):
+                 weight_offset: float = 0.0, weight_name: str = "weight"):
         super().__init__(runtime, prefix)
         self.width, self.eps, self.init = int(width), float(eps), tuple(init)
         self.weight_offset = float(weight_offset)
+        self.weight_name = weight_name           # the tensor is `<prefix><weight_name>`
         self.weight = None
 
     def own_tensor_specs(self):
-        return {self.prefix + "weight": TensorSpec((self.width,), init=self.init)}
+        return {self.prefix + self.weight_name: TensorSpec((self.width,), init=self.init)}
 
     def own_bind(self, tensors):
-        self.weight = tensors[self.prefix + "weight"]
+        self.weight = tensors[self.prefix + self.weight_name]
 
     def own_weights(self):
         return [self.weight]
 
-    def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1):
-        if n_partials == 0:                  # the stream already holds the sum
-            delta = None
+    def add_norm(self, ctx, x, delta, out, rows=None, n_partials: int = 1, delta_norm=None):
+        """delta_norm (an RMSNorm, optional): the delta is normalised by it before it joins the stream, in the same
+        kernel (blocks that put a norm behind each sublayer).  out = None: the stream is updated and nothing else."""
+        if n_partials == 0 or delta is None:     # the stream already holds the sum
+            delta, delta_norm = None, None
         stride = ctx.delta_slabs.stride(0) if n_partials > 1 else 0
+        if delta_norm is not None:
+            ops.norm_add_rms_norm(x, delta, delta_norm.weight, delta_norm.eps, delta_norm.weight_offset,
+                                  self.weight if out is not None else None, self.eps, out, rows=rows,
+                                  n_partials=n_partials, n_rows=ctx.n_tokens, partial_stride=stride,
+                                  weight_offset=self.weight_offset)
+            return
+        if out is None:
+            raise ValueError("add_norm without an output needs a delta that passes through a norm of its own")
         ops.add_rms_norm(x, delta, self.weight, self.eps, out, rows=rows, n_partials=n_partials,
                          n_rows=ctx.n_tokens, partial_stride=stride, weight_offset=self.weight_offset)
 

@@ -38,7 +38,7 @@ class TensorSpec:
 class PartSpec:
     """A part by category and kind, its parameters, and the prefix of its
     tensor names in the weight file."""
-    category: str            # 'mixer' | 'feed_forward' | 'norm' | 'position' | 'block' | 'embedding' | 'head'
+    category: str            # 'mixer' | 'feed_forward' | 'norm' | 'position' | 'block' | 'embedding' | 'head' | 'reentry'
     kind: str
     params: dict = field(default_factory=dict)
     prefix: str = ""
@@ -48,9 +48,12 @@ class PartSpec:
 class LayerCall:
     """One entry of the run order: run `layer`; if `cache_from` is given, the
     mixer writes nothing and reads the cache that the earlier call with that
-    index in the order list owns."""
+    index in the order list owns.  `reenter`: before this call the model's re-entry part (ModelSpec.reentry)
+    replaces the stream by a map of the stream and of the embedding output (a looped stretch of layers that takes
+    the embedding in again at the start of every pass)."""
     layer: int
     cache_from: Optional[int] = None
+    reenter: bool = False
 
 
 @dataclass
@@ -63,8 +66,11 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     max_positions: Optional[int] = None
+    reentry: Optional[PartSpec] = None     # category 'reentry': what LayerCall.reenter runs
 
     def validate(self) -> None:
+        if any(call.reenter for call in self.order) and self.reentry is None:
+            raise ValueError("a layer call re-enters the embedding output, but the model names no re-entry part")
         for i, call in enumerate(self.order):
             if not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"order[{i}] names layer {call.layer}, the model has {len(self.layers)}")
