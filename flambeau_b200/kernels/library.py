@@ -46,6 +46,11 @@ _SIGNATURES = {
                                     STREAM]),
     "fb_diff_attention_simt": (I, [P, L, P, L, I, P, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, F, F, F, F, P,
                                    STREAM]),
+    # diff_attention_mma.cu
+    "fb_diff_attention_scratch_floats": (L, [I, I, I, I]),
+    "fb_diff_attention_splits": (I, [I, I, I]),
+    "fb_diff_attention_mma": (I, [P, L, P, L, P, P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
+                                  P, L, P, STREAM]),
     # attention_mma.cu
     "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P, L, P, L,
                                    L, I, P, STREAM]),

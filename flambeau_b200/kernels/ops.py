@@ -558,11 +558,72 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
                              score_slopes=score_slopes)
 
 
+def diff_attention_mma_supported(q: torch.Tensor, nh: int, nkv: int, kd: int, vd: int) -> bool:
+    """Whether the tensor-core arrangements take this geometry: bfloat16, key size (per map) a multiple of 16 up to
+    128, value size a multiple of 16 up to 256."""
+    return (q.dtype == torch.bfloat16 and kd % 16 == 0 and 16 <= kd <= 128 and vd % 16 == 0 and 16 <= vd <= 256
+            and nh % nkv == 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def diff_attention_mma(q, out, gate, cache, seq_q_start, seq_q_len, seq_pos_start, n_seqs: int, max_q_len: int,
+                       max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int, kd: int, vd: int,
+                       window: int, scale: float, lam: float, eps: float, out_scale: float, status, alloc=None) -> None:
+    """Differential attention on the tensor cores (csrc/diff_attention_mma.cu).  Sequences are described per entry of
+    the step (first row, rows, first position); any_short / any_long say whether the step holds sequences with
+    rows * (nh / nkv) <= 16 / > 16, which run in the split-key and in the portion arrangement.  `alloc(n)` returns
+    n float32 of scratch for the split arrangement's partials (default: a fresh tensor)."""
+    _cuda(q, out, gate, seq_q_start, seq_q_len, seq_pos_start, status)
+    k_pool, v_pool = cache.k_pool, cache.v_pool
+    n_pages = k_pool.shape[0]
+    n = q.shape[0]
+    if q.shape[1] != nh * 2 * kd or tuple(out.shape) != (n, nh * vd) or tuple(k_pool.shape[1:]) != (nkv, cache.page_size, 2 * kd) \
+            or tuple(v_pool.shape[1:]) != (nkv, cache.page_size, vd):
+        raise KernelError("diff attention: shapes do not match the head counts")
+    if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16):
+        raise KernelError("diff_attention_mma: q, out and the cache must be bfloat16")
+    if not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("diff attention: cache pools must be contiguous")
+    if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (n, nh) or not gate.is_contiguous()):
+        raise KernelError("diff attention: the gate wants contiguous float32 [n, heads]")
+    splits, scratch = 1, None
+    if any_short:
+        max_keys = min(max_kv_len, window + 16) if window > 0 else max_kv_len
+        splits = lib().fb_diff_attention_splits(n_seqs, nkv, max(1, int(max_keys)))
+        floats = lib().fb_diff_attention_scratch_floats(n_seqs, nkv, vd, splits)
+        scratch = alloc(floats) if alloc is not None else torch.empty(floats, dtype=torch.float32, device=q.device)
+    check(lib().fb_diff_attention_mma(
+        q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), _ptr(gate), k_pool.data_ptr(), v_pool.data_ptr(),
+        cache.page_size, n_pages, cache.block_table.data_ptr(), cache.block_table.stride(0), _ptr(cache.table_base),
+        seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_pos_start.data_ptr(), n_seqs, max_q_len,
+        1 if any_short else 0, 1 if any_long else 0, nh, nkv, kd, vd, int(window), float(scale), float(lam),
+        float(eps), float(out_scale), splits, _ptr(scratch), scratch.numel() if scratch is not None else 0,
+        status.data_ptr(), _stream()), "diff_attention_mma")
+
+
 def diff_attention(ctx, q, out, gate, cache, nh: int, nkv: int, kd: int, vd: int, window: int, scale: float,
                    lam: float, eps: float, out_scale: float) -> None:
     """Differential attention of every row of the step over its request's cached keys and values, with the kernel
-    that fits the dtype and the sizes: the float32-math kernel for the 32-bit mode and for sizes the tensor-core
-    arrangements do not take."""
+    that fits the dtype and the sizes: the tensor-core arrangements for bfloat16 and sizes they take, the
+    float32-math kernel otherwise (all of the 32-bit mode)."""
     b = ctx.batch
-    diff_attention_simt(q, out, gate, cache, b.positions, b.row_seq, nh, nkv, kd, vd, window, scale, lam, eps,
-                        out_scale, ctx.runtime.status)
+    if diff_attention_mma_supported(q, nh, nkv, kd, vd) and _DIFF_MMA[0]:
+        G = nh // nkv
+        short = [ql * G <= 16 for ql in b.seq_q_len]
+        diff_attention_mma(q, out, gate, cache, b.seq_q_start_d, b.seq_q_len_d, b.seq_pos_start_d, b.n_seqs,
+                           b.max_q_len, b.max_kv_len, any(short), not all(short), nh, nkv, kd, vd, window, scale, lam,
+                           eps, out_scale, ctx.runtime.status,
+                           alloc=lambda n: ctx.ws.alloc((n,), torch.float32))
+    else:
+        diff_attention_simt(q, out, gate, cache, b.positions, b.row_seq, nh, nkv, kd, vd, window, scale, lam, eps,
+                            out_scale, ctx.runtime.status)
+
+
+import os as _os
+
+_DIFF_MMA = [_os.environ.get("FLAMBEAU_DIFF_ATTN_MMA", "1") != "0"]
+
+
+def set_diff_attention_mma(on: bool) -> None:
+    """Differential attention in bfloat16 on the tensor-core arrangements where they take the geometry (the default),
+    or always on the float32-math kernel."""
+    _DIFF_MMA[0] = bool(on)

@@ -8,8 +8,12 @@ Notation: n tokens, D = width, H query heads, G key/value heads, d = per-map que
 """
 from __future__ import annotations
 
+import json
 import math
+import struct
+from pathlib import Path
 
+import numpy as np
 import torch
 
 F64 = torch.float64
@@ -39,11 +43,12 @@ def dense_ff(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def window_mask(n, size):
-    """[n, n] bool: query i sees key j when 0 <= i - j < size."""
-    i = torch.arange(n)[:, None]
-    j = torch.arange(n)[None, :]
-    return (i - j >= 0) & (i - j < size)
+def window_mask(positions, n_keys, size):
+    """[queries, n_keys] bool: the query at position p sees key j when 0 <= p - j < size (size 0: every j <= p)."""
+    i = torch.as_tensor(positions, dtype=torch.long)[:, None]
+    j = torch.arange(n_keys)[None, :]
+    seen = i - j >= 0
+    return seen & (i - j < size) if size else seen
 
 
 def softmax_map(q, k, v, scale, mask):
@@ -57,6 +62,21 @@ def lambda_of(w, p, diff):
     return math.exp(float((w[p + "lq1"] * w[p + "lk1"]).sum())) - math.exp(float((w[p + "lq2"] * w[p + "lk2"]).sum())) + diff
 
 
+def diff_heads(q, k, v, gate, positions, *, scale, window, lam, diff, eps):
+    """The heads' outputs, concatenated: q [n, H, 2, d] for queries at `positions`, k [T, G, 2, d] and v [T, G, e]
+    for the keys at 0 .. T-1, gate [n, H] or None.  Returns [n, H * e]."""
+    H, G = q.shape[1], k.shape[1]
+    mask = window_mask(positions, k.shape[0], window)
+    heads = []
+    for hh in range(H):
+        g = hh // (H // G)
+        a1 = softmax_map(q[:, hh, 0], k[:, g, 0], v[:, g], scale, mask)
+        a2 = softmax_map(q[:, hh, 1], k[:, g, 1], v[:, g], scale, mask)
+        o = unit_rms(a1 - lam * a2, eps) * (1.0 - diff)
+        heads.append(o if gate is None else o * gate[:, hh:hh + 1])
+    return torch.cat(heads, dim=-1)
+
+
 def differential_attention(h, w, p, m, eps):
     """The attention mixer: two softmax maps per head over shared values, their difference normalised per head,
     gated per head, projected.  h [n, D]; m = the layer's 'mixer' object of the configuration."""
@@ -66,16 +86,9 @@ def differential_attention(h, w, p, m, eps):
     k = (h @ w[p + "k"].T + w[p + "k.b"]).view(n, G, 2, d)
     v = (h @ w[p + "v"].T + w[p + "v.b"]).view(n, G, e)
     gate = torch.sigmoid(h @ w[p + "g"].T)                      # [n, H]
-    lam = lambda_of(w, p, m["diff"])
-    mask = window_mask(n, m["mask"]["size"])
-    heads = []
-    for hh in range(H):
-        g = hh // (H // G)
-        a1 = softmax_map(q[:, hh, 0], k[:, g, 0], v[:, g], m["scale"], mask)
-        a2 = softmax_map(q[:, hh, 1], k[:, g, 1], v[:, g], m["scale"], mask)
-        o = unit_rms(a1 - lam * a2, eps) * (1.0 - m["diff"])
-        heads.append(o * gate[:, hh:hh + 1])
-    return torch.cat(heads, dim=-1) @ w[p + "o"].T
+    o = diff_heads(q, k, v, gate, range(n), scale=m["scale"], window=m["mask"]["size"],
+                   lam=lambda_of(w, p, m["diff"]), diff=m["diff"], eps=eps)
+    return o @ w[p + "o"].T
 
 
 # ---- the model ----------------------------------------------------------------------------------------------------
@@ -119,3 +132,32 @@ def forward(cfg, w, tokens, return_layers=False):
         streams.append(x)
     logits = offset_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(streams)) if return_layers else logits
+
+
+# ---- reading a model folder (a parser of its own: 8-byte length, JSON header, data) ----------------------------
+def read_folder(folder):
+    """(config dict, {name: float64 tensor})."""
+    folder = Path(folder)
+    cfg = json.loads((folder / "config.json").read_text())
+    raw = (folder / "model.safetensors").read_bytes()
+    (n,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + n])
+    out = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = info["data_offsets"]
+        buf = np.frombuffer(raw, dtype=np.uint8, count=b - a, offset=8 + n + a)
+        if info["dtype"] == "BF16":
+            t = torch.from_numpy((buf.view(np.uint16).astype(np.uint32) << 16).view(np.float32).copy())
+        elif info["dtype"] == "F32":
+            t = torch.from_numpy(buf.view(np.float32).copy())
+        else:
+            raise ValueError(f"{name}: dtype {info['dtype']}")
+        out[name] = t.to(F64).view(info["shape"])
+    return cfg, out
+
+
+def argmax_lowest(row):
+    """The lowest index among the largest entries."""
+    return int((row == row.max()).nonzero()[0])
