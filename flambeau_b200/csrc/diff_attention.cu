@@ -65,6 +65,86 @@ __global__ void qkv_bias_cache_write_kernel(const float* __restrict__ proj, long
     }
 }
 
+// The same four columns at a time (head sizes multiples of 4, aligned rows): grid (tokens, ceil(items / 256)), an
+// item being four consecutive q, k or v columns; the gate columns follow as single items.
+template <typename T> struct Row4 {};
+template <> struct Row4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Row4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename TB, typename T>
+__global__ void __launch_bounds__(256)
+qkv_bias_cache_write_vec_kernel(const float* __restrict__ proj, long proj_stride, int n_partials, long partial_stride,
+                                const TB* __restrict__ bias, T* __restrict__ q_out, long q_out_stride,
+                                float* __restrict__ gate_out, const int* __restrict__ positions,
+                                const int* __restrict__ row_seq, const int* __restrict__ block_table, int table_stride,
+                                const int* __restrict__ table_base, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                int page_size, int n_pages, int nh, int nkv, int qd, int vd, int n_gate, int write_kv,
+                                int* status) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int t = blockIdx.x;
+    const int qw = nh * qd, kw = nkv * qd, vw = nkv * vd;
+    const int vec_items = (qw + kw + vw) >> 2;
+    const int item = blockIdx.y * blockDim.x + threadIdx.x;
+    if (item >= vec_items + n_gate) return;
+    if (item >= vec_items) {                                   // a gate column
+        const int c = qw + kw + vw + (item - vec_items);
+        const float* src = proj + (size_t)t * proj_stride + c;
+        float val = 0.0f;
+        for (int p = 0; p < n_partials; ++p) val += src[(size_t)p * partial_stride];
+        gate_out[(size_t)t * n_gate + (item - vec_items)] = 1.0f / (1.0f + expf(-val));
+        return;
+    }
+    const int c = item << 2;
+    if (c >= qw && !write_kv) return;
+    const float* src = proj + (size_t)t * proj_stride + c;
+    float4 val = Row4<float>::load(src);
+    for (int p = 1; p < n_partials; ++p) {
+        const float4 e = Row4<float>::load(src + (size_t)p * partial_stride);
+        val.x += e.x; val.y += e.y; val.z += e.z; val.w += e.w;
+    }
+    if (bias) {
+        const float4 b = Row4<TB>::load(bias + c);
+        val.x += b.x; val.y += b.y; val.z += b.z; val.w += b.w;
+    }
+    if (c < qw) {
+        Row4<T>::store(q_out + (size_t)t * q_out_stride + c, val);
+        return;
+    }
+    const int pos = positions[t], seq = row_seq[t];
+    const int entry = pos / page_size - (table_base ? table_base[seq] : 0);
+    const int page = (entry >= 0 && entry < table_stride) ? block_table[(size_t)seq * table_stride + entry] : -1;
+    if (page < 0 || page >= n_pages) {
+        atomicOr(status, FB_STATUS_BAD_PAGE);
+        return;
+    }
+    const int slot = pos % page_size;
+    if (c < qw + kw) {
+        const int j = c - qw, h = j / qd, d = j - h * qd;
+        Row4<T>::store(k_pool + (((size_t)page * nkv + h) * page_size + slot) * qd + d, val);
+    } else {
+        const int j = c - qw - kw, h = j / vd, d = j - h * vd;
+        Row4<T>::store(v_pool + (((size_t)page * nkv + h) * page_size + slot) * vd + d, val);
+    }
+}
+
 FB_API int fb_qkv_bias_cache_write(const float* proj, long long proj_stride, int n_partials, long long partial_stride,
                                    const void* bias, int bias_dtype, void* q_out, long long q_out_stride,
                                    int out_dtype, float* gate_out, const int* positions, const int* row_seq,
@@ -80,6 +160,18 @@ FB_API int fb_qkv_bias_cache_write(const float* proj, long long proj_stride, int
     const int cols = nh * qd + nkv * qd + nkv * vd + n_gate;
     FB_REQUIRE(proj_stride >= cols, "qkv_bias_cache_write: rows of %lld for %d columns", proj_stride, cols);
     if (!bias) bias_dtype = FB_F32;
+    const bool vec = qd % 4 == 0 && vd % 4 == 0 && proj_stride % 4 == 0 && partial_stride % 4 == 0 &&
+                     q_out_stride % 4 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)bias % 16 == 0 &&
+                     (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0;
+    if (vec) {
+        const int items = (cols - n_gate) / 4 + n_gate;
+        FB_DISPATCH_DTYPE(bias_dtype, TB, FB_DISPATCH_DTYPE(out_dtype, T,
+            (fb_launch((qkv_bias_cache_write_vec_kernel<TB, T>), dim3(n, (items + 255) / 256), 256, 0, stream, proj,
+                       (long)proj_stride, n_partials, (long)partial_stride, (const TB*)bias, (T*)q_out,
+                       (long)q_out_stride, gate_out, positions, row_seq, block_table, table_stride, table_base,
+                       (T*)k_pool, (T*)v_pool, page_size, n_pages, nh, nkv, qd, vd, n_gate, write_kv, status))));
+        return fb_check_launch("qkv_bias_cache_write");
+    }
     FB_DISPATCH_DTYPE(bias_dtype, TB, FB_DISPATCH_DTYPE(out_dtype, T,
         (fb_launch((qkv_bias_cache_write_kernel<TB, T>), dim3(n, (cols + 255) / 256), 256, 0, stream, proj,
                    (long)proj_stride, n_partials, (long)partial_stride, (const TB*)bias, (T*)q_out, (long)q_out_stride,

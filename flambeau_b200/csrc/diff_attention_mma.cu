@@ -17,8 +17,9 @@
 //
 // The softmax weights stay float32 into the second product: a weight p is fed as two bfloat16 terms, p_hi = bf16(p)
 // and p_lo = bf16(p - p_hi), so P V carries 16 bits of p's mantissa instead of 8 (two MMAs where a kernel that
-// rounds P issues one).  K/V tiles arrive by 16-byte cp.async copies through two stages; rows outside the visible
-// range or without a page are zero-filled.
+// rounds P issues one).  K/V tiles arrive by 16-byte cp.async copies through three stages where shared memory has
+// room (two tiles in flight while one is used; one barrier a tile), else two; rows outside the visible range or
+// without a page are zero-filled.  Tiles that all rows of a warp see whole skip the mask.
 #include "attention_common.cuh"
 
 namespace {
@@ -31,12 +32,14 @@ struct DiffArgs {
     const float* gate;                   // [rows of the step][nh], or nullptr
     const __nv_bfloat16* k_pool; const __nv_bfloat16* v_pool;
     int page_size, n_pages;
+    int page_shift;                      // log2(page_size) where it is a power of two, else -1
     const int* block_table; int table_stride; const int* table_base;
     const int* seq_q_start; const int* seq_q_len; const int* seq_pos_start;
     int n_seqs, nh, nkv, kd, vd, window;
     float scale_log2e, lambda, eps, out_scale;
     int short_rows;                      // sequences with q_len * HG <= short_rows run in the split arrangement
     int n_splits;                        // split arrangement: CTAs per (sequence, key/value head)
+    int n_stages;                        // K/V tiles in shared memory (2 or 3)
     float* part_o; float* part_ml;       // partials: [slot][sequence][g][16 rows][2 maps] x vd, and x 2 (maximum, sum)
     int* status;
 };
@@ -65,7 +68,7 @@ diff_attention_mma_kernel(const DiffArgs a) {
     const int q_len = a.seq_q_len[seq];
     const int rows_total = q_len * HG;
     if ((rows_total <= a.short_rows) != SPLIT) return;
-    const int R0 = SPLIT ? 0 : blockIdx.x * 64;
+    const int R0 = SPLIT ? 0 : (gridDim.x - 1 - blockIdx.x) * 64;   // the tiles that see the most keys start first
     if (R0 >= rows_total) return;
     const int R1 = min(R0 + QROWS, rows_total) - 1;
     const int q_start = a.seq_q_start[seq], pos_start = a.seq_pos_start[seq];
@@ -89,8 +92,9 @@ diff_attention_mma_kernel(const DiffArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int KDP = kd + 8, KP = 2 * kd + 8, VP = vd + 8;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [2 maps][QROWS][KDP]
-    __nv_bfloat16* Ks = Qs + 2 * QROWS * KDP;                              // [2 stages][64][KP]
-    __nv_bfloat16* Vs = Ks + 2 * KT * KP;                                  // [2 stages][64][VP]
+    const int NS = a.n_stages;
+    __nv_bfloat16* Ks = Qs + 2 * QROWS * KDP;                              // [stages][64][KP]
+    __nv_bfloat16* Vs = Ks + (size_t)NS * KT * KP;                         // [stages][64][VP]
 
     // ---- Q: rows of both maps, 16 bytes at a time; rows past the end are zero ----
     {
@@ -116,31 +120,36 @@ diff_attention_mma_kernel(const DiffArgs a) {
         bool ok = t >= t_lo && t <= t_hi;
         size_t cache_row = 0;
         if (ok) {
-            const int e = t / a.page_size - base_page;
+            const int lp = a.page_shift >= 0 ? t >> a.page_shift : t / a.page_size;
+            const int slot = a.page_shift >= 0 ? t & (a.page_size - 1) : t - lp * a.page_size;
+            const int e = lp - base_page;
             const int page = (e >= 0 && e < a.table_stride) ? table[e] : -1;
             if (page < 0 || page >= a.n_pages) {
                 atomicOr(a.status, FB_STATUS_BAD_PAGE);
                 ok = false;
             } else {
-                cache_row = ((size_t)page * a.nkv + g) * a.page_size + (t % a.page_size);
+                cache_row = ((size_t)page * a.nkv + g) * a.page_size + slot;
             }
         }
-        __nv_bfloat16* kdst = Ks + ((size_t)stage * KT + r) * KP;
-        __nv_bfloat16* vdst = Vs + ((size_t)stage * KT + r) * VP;
-        const __nv_bfloat16* ksrc = a.k_pool + cache_row * (2 * kd);
-        const __nv_bfloat16* vsrc = a.v_pool + cache_row * vd;
-        for (int ch = sub; ch < kd / 4; ch += 4) {
-            if (ok) cp_async16(kdst + ch * 8, ksrc + ch * 8);
-            else *reinterpret_cast<uint4*>(kdst + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
+        __nv_bfloat16* kdst = Ks + ((size_t)stage * KT + r) * KP + sub * 8;
+        __nv_bfloat16* vdst = Vs + ((size_t)stage * KT + r) * VP + sub * 8;
+        if (ok) {
+            const __nv_bfloat16* ksrc = a.k_pool + cache_row * (2 * kd) + sub * 8;
+            const __nv_bfloat16* vsrc = a.v_pool + cache_row * vd + sub * 8;
+            for (int ch = sub; ch < kd / 4; ch += 4, kdst += 32, ksrc += 32) cp_async16(kdst, ksrc);
+            for (int ch = sub; ch < vd / 8; ch += 4, vdst += 32, vsrc += 32) cp_async16(vdst, vsrc);
+        } else {
+            for (int ch = sub; ch < kd / 4; ch += 4, kdst += 32) *reinterpret_cast<uint4*>(kdst) = make_uint4(0u, 0u, 0u, 0u);
+            for (int ch = sub; ch < vd / 8; ch += 4, vdst += 32) *reinterpret_cast<uint4*>(vdst) = make_uint4(0u, 0u, 0u, 0u);
         }
-        for (int ch = sub; ch < vd / 8; ch += 4) {
-            if (ok) cp_async16(vdst + ch * 8, vsrc + ch * 8);
-            else *reinterpret_cast<uint4*>(vdst + ch * 8) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        cp_async_commit();
     };
 
-    if (tile_first <= tile_last) load_tile(0, tile_first);
+    // one copy group per tile, in tile order, also where there is no tile left (an empty group): the wait below
+    // can then always name the tile it needs by how many groups may still be pending
+    for (int s = 0; s < NS - 1; ++s) {
+        if (tile_first + s <= tile_last) load_tile(s, tile_first + s);
+        cp_async_commit();
+    }
     __syncthreads();                                                       // Q is in shared memory
 
     // ---- this thread's two rows (lane / 4 and lane / 4 + 8 of the warp's 16) ----
@@ -165,15 +174,20 @@ diff_attention_mma_kernel(const DiffArgs a) {
     for (int vt = 0; vt < VTILES; ++vt) o[vt][0] = o[vt][1] = o[vt][2] = o[vt][3] = 0.0f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
+    // the warp's rows see every key of a tile when the tile lies between the last row's window start and the first
+    // row's position: such tiles need no mask
+    const int warp_R0 = R0 + row_tile * 16;
+    const bool warp_full = warp_R0 + 15 < rows_total;
+    const int warp_p_min = pos_start + warp_R0 / HG;
+    const int warp_lo_max = W > 0 ? max(0, pos_start + min(warp_R0 + 15, rows_total - 1) / HG - W + 1) : 0;
+
     for (int kt = tile_first; kt <= tile_last; ++kt) {
-        const int stage = (kt - tile_first) & 1;
-        if (kt + 1 <= tile_last) {
-            load_tile(stage ^ 1, kt + 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int it = kt - tile_first;
+        const int stage = it % NS;
+        if (NS == 3) cp_async_wait<1>(); else cp_async_wait<0>();          // tile kt has landed ...
+        __syncthreads();                                                   // ... for all threads, and tile kt-1 is done with
+        if (kt + NS - 1 <= tile_last) load_tile((it + NS - 1) % NS, kt + NS - 1);
+        cp_async_commit();
         const __nv_bfloat16* Kt = Ks + (size_t)stage * KT * KP;
         const __nv_bfloat16* Vt = Vs + (size_t)stage * KT * VP;
 
@@ -196,38 +210,54 @@ diff_attention_mma_kernel(const DiffArgs a) {
         }
         // scale (to base-2 units), mask, row maxima
         float tmax[2] = {-INFINITY, -INFINITY};
+        const int key0 = kt * KT + koff;
+        // (scores stay as the product left them; the scale, positive, enters with the exponent below)
+        if (warp_full && key0 + NT * 8 - 1 <= warp_p_min && key0 >= warp_lo_max) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = e >> 1;
-                const int t = kt * KT + koff + nt * 8 + 2 * (lane & 3) + (e & 1);
-                const bool visible = row_ok[i] && t <= row_p[i] && t >= row_lo[i];
-                s[nt][e] = visible ? s[nt][e] * a.scale_log2e : -INFINITY;
-                tmax[i] = fmaxf(tmax[i], s[nt][e]);
+                for (int e = 0; e < 4; ++e) tmax[e >> 1] = fmaxf(tmax[e >> 1], s[nt][e]);
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int t = key0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                    const bool visible = row_ok[i] && t <= row_p[i] && t >= row_lo[i];
+                    s[nt][e] = visible ? s[nt][e] : -INFINITY;
+                    tmax[i] = fmaxf(tmax[i], s[nt][e]);
+                }
             }
         }
+        // m is kept in base-2 units (score * scale * log2 e)
         float corr[2], m_use[2];
+        bool grew = false;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
             tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
-            const float m_new = fmaxf(m[i], tmax[i]);
+            const float m_new = fmaxf(m[i], tmax[i] * a.scale_log2e);
             m_use[i] = m_new == -INFINITY ? 0.0f : m_new;
+            grew = grew || m_new != m[i];
             corr[i] = exp2f(m[i] - m_use[i]);               // 0 while nothing has been seen
             m[i] = m_new;
-            l[i] *= corr[i];
         }
+        if (__any_sync(0xffffffffu, grew)) {               // once the maxima have settled nothing is rescaled
+            l[0] *= corr[0];
+            l[1] *= corr[1];
 #pragma unroll
-        for (int vt = 0; vt < VTILES; ++vt) {
-            o[vt][0] *= corr[0]; o[vt][1] *= corr[0];
-            o[vt][2] *= corr[1]; o[vt][3] *= corr[1];
+            for (int vt = 0; vt < VTILES; ++vt) {
+                o[vt][0] *= corr[0]; o[vt][1] *= corr[0];
+                o[vt][2] *= corr[1]; o[vt][3] *= corr[1];
+            }
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float p = exp2f(s[nt][e] - m_use[e >> 1]);
+                const float p = exp2f(fmaf(s[nt][e], a.scale_log2e, -m_use[e >> 1]));
                 s[nt][e] = p;
                 l[e >> 1] += p;
             }
@@ -257,7 +287,6 @@ diff_attention_mma_kernel(const DiffArgs a) {
                 }
             }
         }
-        __syncthreads();                                   // the stage may be refilled
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -287,6 +316,7 @@ diff_attention_mma_kernel(const DiffArgs a) {
     }
 
     // ---- epilogue of a portion: map 2 hands a2 = O2 / l2 over, map 1 forms the head's output ----
+    __syncthreads();                                       // every warp is done with the last tile
     float* X = reinterpret_cast<float*>(Vs);               // [64 rows][vd]; the tiles are no longer needed
     const float inv[2] = {l[0] > 0.0f ? 1.0f / l[0] : 0.0f, l[1] > 0.0f ? 1.0f / l[1] : 0.0f};
     if (map == 1) {
@@ -330,8 +360,9 @@ diff_attention_mma_kernel(const DiffArgs a) {
     }
 }
 
-// One warp per (sequence, key/value head, row) of the split arrangement: merges the partials of all slots for both
-// maps and runs the epilogue.  NDR = ceil(vd / 32) values per lane.
+// One warp per (sequence, key/value head, row) of the split arrangement: merges the partials of all slots (at most
+// 32: lane s holds slot s's maximum and sum) for both maps and runs the epilogue.  NDR = ceil(vd / 32) values per
+// lane.  The partial outputs are fetched eight slots at a time, all loads issued before the first use.
 template <int NDR>
 __global__ void __launch_bounds__(128)
 diff_attention_combine_kernel(const DiffArgs a, int n_slots) {
@@ -345,24 +376,37 @@ diff_attention_combine_kernel(const DiffArgs a, int n_slots) {
     const int rows_total = a.seq_q_len[seq] * HG;
     if (rows_total > a.short_rows || r >= rows_total) return;
     const int vd = a.vd;
+    const size_t slot_stride = (size_t)a.n_seqs * a.nkv * 16 * 2;       // partials from one slot to the next
     float res[2][NDR];
 #pragma unroll
     for (int mp = 0; mp < 2; ++mp) {
-        float M = -INFINITY;
-        for (int s = 0; s < n_slots; ++s) M = fmaxf(M, a.part_ml[2 * part_index(a, s, seq, g, r, mp)]);
-        float L = 0.0f;
+        const size_t at0 = part_index(a, 0, seq, g, r, mp);
+        float ms = -INFINITY, ls = 0.0f;
+        if (lane < n_slots) {
+            ms = a.part_ml[2 * (at0 + lane * slot_stride)];
+            ls = a.part_ml[2 * (at0 + lane * slot_stride) + 1];
+        }
+        const float M = fb_warp_max(ls > 0.0f ? ms : -INFINITY);
+        const float w = ls > 0.0f ? exp2f(ms - M) : 0.0f;               // this lane's slot's weight
+        const float L = fb_warp_sum(w * ls);
 #pragma unroll
         for (int d = 0; d < NDR; ++d) res[mp][d] = 0.0f;
-        for (int s = 0; s < n_slots; ++s) {
-            const size_t at = part_index(a, s, seq, g, r, mp);
-            const float ls = a.part_ml[2 * at + 1];
-            if (!(ls > 0.0f)) continue;
-            const float w = exp2f(a.part_ml[2 * at] - M);
-            L += w * ls;
-            const float* po = a.part_o + at * vd;
+        for (int s0 = 0; s0 < n_slots; s0 += 8) {
+            float val[8][NDR];
 #pragma unroll
-            for (int d = 0; d < NDR; ++d)
-                if (lane + 32 * d < vd) res[mp][d] += w * po[lane + 32 * d];
+            for (int u = 0; u < 8; ++u) {
+                const float* po = a.part_o + (at0 + (size_t)min(s0 + u, n_slots - 1) * slot_stride) * vd;
+#pragma unroll
+                for (int d = 0; d < NDR; ++d) val[u][d] = lane + 32 * d < vd ? po[lane + 32 * d] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float wu = __shfl_sync(0xffffffffu, w, min(s0 + u, n_slots - 1));
+                if (s0 + u < n_slots && wu > 0.0f) {
+#pragma unroll
+                    for (int d = 0; d < NDR; ++d) res[mp][d] = fmaf(wu, val[u][d], res[mp][d]);
+                }
+            }
         }
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
 #pragma unroll
@@ -383,26 +427,44 @@ diff_attention_combine_kernel(const DiffArgs a, int n_slots) {
         if (lane + 32 * d < vd) op[lane + 32 * d] = __float2bfloat16_rn(res[0][d] * f);
 }
 
+constexpr size_t SMEM_LIMIT = 200 * 1024;
+
+size_t smem_bytes(int kd, int vd, bool split, int stages) {
+    const int qrows = split ? 16 : 64;
+    return ((size_t)2 * qrows * (kd + 8) + (size_t)stages * KT * (2 * kd + 8) + (size_t)stages * KT * (vd + 8)) *
+           sizeof(__nv_bfloat16);
+}
+// Three tiles in shared memory where they fit (two in flight while one is used), else two.  The split arrangement
+// streams the cache and keeps three only while two CTAs still fit on a multiprocessor.
+int stages_for(int kd, int vd, bool split) {
+    const size_t three = smem_bytes(kd, vd, split, 3);
+    return three <= (split ? SMEM_LIMIT / 2 + 8 * 1024 : SMEM_LIMIT) ? 3 : 2;
+}
+
 template <int KSTEPS, int VTILES, bool SPLIT>
-int launch_diff_mma(const DiffArgs& a, dim3 grid, cudaStream_t stream) {
-    const int qrows = SPLIT ? 16 : 64;
-    const size_t smem = ((size_t)2 * qrows * (a.kd + 8) + (size_t)2 * KT * (2 * a.kd + 8) + (size_t)2 * KT * (a.vd + 8)) *
-                        sizeof(__nv_bfloat16);
+int launch_diff_mma(const DiffArgs& a, dim3 grid, cudaStream_t stream, int* resident) {
+    const size_t smem = smem_bytes(a.kd, a.vd, SPLIT, a.n_stages);
     auto kern = diff_attention_mma_kernel<KSTEPS, VTILES, SPLIT>;
     static bool raised[FB_MAX_DEVICES] = {};
     if (fb_needs_setup(raised)) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
             return fb_fail(-1, "diff attention: cannot raise the shared-memory limit");
         fb_setup_done(raised);
     }
-    if (smem > 200 * 1024) return fb_fail(-1, "diff attention: %zu bytes of shared memory", smem);
+    if (smem > SMEM_LIMIT) return fb_fail(-1, "diff attention: %zu bytes of shared memory", smem);
+    if (resident) {                       // asked only how many CTAs of this arrangement a multiprocessor holds
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 256, smem) != cudaSuccess || n < 1) n = 1;
+        *resident = n;
+        return 0;
+    }
     fb_launch(kern, grid, 256, smem, stream, a);
     return fb_check_launch(SPLIT ? "diff_attention_split" : "diff_attention_portions");
 }
 
 template <bool SPLIT>
-int dispatch_diff_mma(const DiffArgs& a, dim3 grid, cudaStream_t stream) {
-#define FB_DIFF_MMA(KS, VT) return launch_diff_mma<KS, VT, SPLIT>(a, grid, stream)
+int dispatch_diff_mma(const DiffArgs& a, dim3 grid, cudaStream_t stream, int* resident = nullptr) {
+#define FB_DIFF_MMA(KS, VT) return launch_diff_mma<KS, VT, SPLIT>(a, grid, stream, resident)
     if (a.kd <= 64) {
         if (a.vd <= 64) FB_DIFF_MMA(4, 8);
         if (a.vd <= 128) FB_DIFF_MMA(4, 16);
@@ -422,13 +484,20 @@ FB_API long long fb_diff_attention_scratch_floats(int n_seqs, int nkv, int vd, i
 }
 
 // How many CTAs per (sequence, key/value head) the split arrangement uses for a step of `n_seqs` sequences whose
-// rows see at most `max_keys` keys: enough to fill the device twice, at most one per key tile, at most 16.
-FB_API int fb_diff_attention_splits(int n_seqs, int nkv, int max_keys) {
+// rows see at most `max_keys` keys: as many as are resident on the device at once (a CTA beyond that would run in a
+// second round behind the others), at most one per key tile, at most 8 (four partials each: the combining kernel
+// holds one partial's weight per lane).
+FB_API int fb_diff_attention_splits(int n_seqs, int nkv, int max_keys, int kd, int vd) {
+    if (kd % 16 || kd < 16 || kd > 128 || vd % 16 || vd < 16 || vd > 256) return 1;
     const int pairs = n_seqs * nkv > 0 ? n_seqs * nkv : 1;
     const int tiles = (max_keys + fb_attn::KT - 1) / fb_attn::KT + 1;
-    int s = (2 * fb_sm_count() + pairs - 1) / pairs;
+    DiffArgs a = {};
+    a.kd = kd; a.vd = vd; a.n_stages = stages_for(kd, vd, true);
+    int resident = 1;
+    if (dispatch_diff_mma<true>(a, dim3(1), nullptr, &resident) != 0) resident = 1;
+    int s = resident * fb_sm_count() / pairs;
     if (s > tiles) s = tiles;
-    if (s > 16) s = 16;
+    if (s > 8) s = 8;
     return s < 1 ? 1 : s;
 }
 
@@ -443,6 +512,7 @@ FB_API int fb_diff_attention_mma(const void* q, long long q_stride, void* out, l
     FB_REQUIRE(kd % 16 == 0 && kd >= 16 && kd <= 128, "diff attention (mma): key size %d is not a multiple of 16 up to 128", kd);
     FB_REQUIRE(vd % 16 == 0 && vd >= 16 && vd <= 256, "diff attention (mma): value size %d is not a multiple of 16 up to 256", vd);
     FB_REQUIRE(page_size > 0 && n_pages > 0 && window >= 0 && eps > 0.0f, "diff attention: bad cache geometry or eps");
+    FB_REQUIRE(scale > 0.0f, "diff attention (mma): the score scale must be positive");
     FB_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)out % 4 == 0 &&
                (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0, "diff attention (mma): unaligned operands");
     FB_REQUIRE(n_seqs <= 65535 && nkv <= 65535, "diff attention: too many sequences or heads for one grid");
@@ -453,16 +523,19 @@ FB_API int fb_diff_attention_mma(const void* q, long long q_stride, void* out, l
     a.gate = gate;
     a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
     a.page_size = page_size; a.n_pages = n_pages;
+    a.page_shift = -1;
+    for (int b = 0; b < 30; ++b) if ((1 << b) == page_size) a.page_shift = b;
     a.block_table = block_table; a.table_stride = table_stride; a.table_base = table_base;
     a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len; a.seq_pos_start = seq_pos_start;
     a.n_seqs = n_seqs; a.nh = nh; a.nkv = nkv; a.kd = kd; a.vd = vd; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f; a.lambda = lambda; a.eps = eps; a.out_scale = out_scale;
     a.short_rows = 16;
-    a.n_splits = n_splits < 1 ? 1 : n_splits;
+    a.n_splits = n_splits < 1 ? 1 : n_splits > 8 ? 8 : n_splits;
     a.part_o = nullptr; a.part_ml = nullptr;
     a.status = status;
     const int HG = nh / nkv;
     if (any_long) {
+        a.n_stages = stages_for(kd, vd, false);
         const long rows = (long)max_q_len * HG;
         const int rc = dispatch_diff_mma<false>(a, dim3((unsigned)((rows + 63) / 64), nkv, n_seqs), stream);
         if (rc) return rc;
@@ -474,6 +547,7 @@ FB_API int fb_diff_attention_mma(const void* q, long long q_stride, void* out, l
         const size_t n_part = (size_t)a.n_splits * 4 * n_seqs * nkv * 16 * 2;
         a.part_o = scratch;
         a.part_ml = scratch + n_part * vd;
+        a.n_stages = stages_for(kd, vd, true);
         const int rc = dispatch_diff_mma<true>(a, dim3(a.n_splits, nkv, n_seqs), stream);
         if (rc) return rc;
         const long items = (long)n_seqs * nkv * 16;

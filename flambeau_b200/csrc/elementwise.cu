@@ -352,6 +352,77 @@ norm_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, 
     }
 }
 
+// The same four elements at a time (width a multiple of 4, 16-byte aligned rows): every load of a thread's part of
+// the row is issued before the first use, so a row costs one round trip to memory per pass.
+template <typename TWD, typename TW, typename TO, int VPT>
+__global__ void __launch_bounds__(1024)
+norm_add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_partials,
+                            size_t partial_stride, const TWD* __restrict__ wd, float eps_d, float wd_offset,
+                            const TW* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows, int H,
+                            float eps, float w_offset) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    __shared__ float red[32];
+    const int j = blockIdx.x;
+    const int r = rows ? rows[j] : j;
+    float* xr = x + (size_t)r * H;
+    const float* dr = delta + (size_t)r * H;
+    const int nvec = H >> 2;
+    float4 v[VPT], d[VPT], wdv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            v[i] = Vec4<float>::load(xr + 4 * c);
+            d[i] = Vec4<float>::load(dr + 4 * c);
+            wdv[i] = Vec4<TWD>::load(wd + 4 * c);
+        } else {
+            v[i] = d[i] = wdv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    for (int p = 1; p < n_partials; ++p) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < nvec) {
+                const float4 e = Vec4<float>::load(dr + (size_t)p * partial_stride + 4 * c);
+                d[i].x += e.x; d[i].y += e.y; d[i].z += e.z; d[i].w += e.w;
+            }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) ss += d[i].x * d[i].x + d[i].y * d[i].y + d[i].z * d[i].z + d[i].w * d[i].w;
+    ss = fb_block_sum(ss, red);
+    const float inv_d = 1.0f / sqrtf(ss / (float)H + eps_d);
+    ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            v[i].x += d[i].x * inv_d * (wdv[i].x + wd_offset);
+            v[i].y += d[i].y * inv_d * (wdv[i].y + wd_offset);
+            v[i].z += d[i].z * inv_d * (wdv[i].z + wd_offset);
+            v[i].w += d[i].w * inv_d * (wdv[i].w + wd_offset);
+            if (!rows) Vec4<float>::store(xr + 4 * c, v[i]);
+        }
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    if (!out) return;
+    ss = fb_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)j * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            const float4 wv = Vec4<TW>::load(w + 4 * c);
+            Vec4<TO>::store(o + 4 * c, make_float4(v[i].x * (wv.x + w_offset) * inv, v[i].y * (wv.y + w_offset) * inv,
+                                                   v[i].z * (wv.z + w_offset) * inv, v[i].w * (wv.w + w_offset) * inv));
+        }
+    }
+}
+
 FB_API int fb_norm_add_rmsnorm(float* x, const float* delta, int n_partials, long long partial_stride,
                                const void* wd, int wd_dtype, float eps_d, float wd_offset, const void* w, int w_dtype,
                                void* out, int out_dtype, const int* rows, int n_out, int H, float eps, float w_offset,
@@ -362,6 +433,24 @@ FB_API int fb_norm_add_rmsnorm(float* x, const float* delta, int n_partials, lon
     FB_REQUIRE(!out || w, "norm_add_rmsnorm: an output needs its weight");
     if (n_out == 0) return 0;
     if (!out) { w = wd; w_dtype = wd_dtype; out_dtype = FB_F32; }
+    const bool aligned = H % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 && partial_stride % 4 == 0 &&
+                         (uintptr_t)wd % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
+    if (aligned) {
+        // hundreds of rows: about 256 threads a row with several vectors each; a few rows: as many threads as vectors
+        const int nvec = H / 4;
+        const int want = n_out >= 128 ? (nvec + 255) / 256 : (nvec + 1023) / 1024;
+        const int vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : want <= 8 ? 8 : 16;
+        const int threads_v = (((nvec + vpt - 1) / vpt) + 31) / 32 * 32;
+#define FB_NANV_CASE(V)                                                                                            \
+        FB_DISPATCH_DTYPE(wd_dtype, TWD, FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, TO,           \
+            (fb_launch((norm_add_rmsnorm_vec_kernel<TWD, TW, TO, V>), n_out, threads_v, 0, stream, x, delta,       \
+                       n_partials, (size_t)partial_stride, (const TWD*)wd, eps_d, wd_offset, (const TW*)w,         \
+                       (TO*)out, rows, H, eps, w_offset)))))
+        if (vpt == 1) FB_NANV_CASE(1); else if (vpt == 2) FB_NANV_CASE(2); else if (vpt == 4) FB_NANV_CASE(4);
+        else if (vpt == 8) FB_NANV_CASE(8);
+        if (vpt <= 8) return fb_check_launch("norm_add_rmsnorm");
+#undef FB_NANV_CASE
+    }
     const int threads = H >= 4096 ? 1024 : H >= 1024 ? 512 : H >= 256 ? 256 : 128;   // H / threads <= 16
     const int vpt = (H + threads - 1) / threads;
 #define FB_NAN_CASE(V)                                                                                             \

@@ -48,7 +48,7 @@ _SIGNATURES = {
                                    STREAM]),
     # diff_attention_mma.cu
     "fb_diff_attention_scratch_floats": (L, [I, I, I, I]),
-    "fb_diff_attention_splits": (I, [I, I, I]),
+    "fb_diff_attention_splits": (I, [I, I, I, I, I]),
     "fb_diff_attention_mma": (I, [P, L, P, L, P, P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
                                   P, L, P, STREAM]),
     # attention_mma.cu

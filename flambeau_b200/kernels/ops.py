@@ -588,7 +588,7 @@ def diff_attention_mma(q, out, gate, cache, seq_q_start, seq_q_len, seq_pos_star
     splits, scratch = 1, None
     if any_short:
         max_keys = min(max_kv_len, window + 16) if window > 0 else max_kv_len
-        splits = lib().fb_diff_attention_splits(n_seqs, nkv, max(1, int(max_keys)))
+        splits = lib().fb_diff_attention_splits(n_seqs, nkv, max(1, int(max_keys)), kd, vd)
         floats = lib().fb_diff_attention_scratch_floats(n_seqs, nkv, vd, splits)
         scratch = alloc(floats) if alloc is not None else torch.empty(floats, dtype=torch.float32, device=q.device)
     check(lib().fb_diff_attention_mma(
@@ -606,7 +606,7 @@ def diff_attention(ctx, q, out, gate, cache, nh: int, nkv: int, kd: int, vd: int
     that fits the dtype and the sizes: the tensor-core arrangements for bfloat16 and sizes they take, the
     float32-math kernel otherwise (all of the 32-bit mode)."""
     b = ctx.batch
-    if diff_attention_mma_supported(q, nh, nkv, kd, vd) and _DIFF_MMA[0]:
+    if diff_attention_mma_supported(q, nh, nkv, kd, vd) and scale > 0.0 and _DIFF_MMA[0]:
         G = nh // nkv
         short = [ql * G <= 16 for ql in b.seq_q_len]
         diff_attention_mma(q, out, gate, cache, b.seq_q_start_d, b.seq_q_len_d, b.seq_pos_start_d, b.n_seqs,

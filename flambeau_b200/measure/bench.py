@@ -28,6 +28,9 @@ A "step" is one decode step.  It prints ONE JSON line:
   shapes     the Mistral-Small-24B shape: decode at batch 1 / 8 / 64 with 4,096-token contexts and a 2,048-token
              prefill, each with its roofline fraction
 
+`--only zedivik` is a line of its own (not part of the default run): the Zedivik design beside Mistral at equal
+size, decode and prefill tokens a second and the kernels that differ (flambeau_b200/measure/compare.py).
+
 The cache of the timed sequences is laid out by the cache manager exactly as a real request of that length
 leaves it (pages taken and, under the window, given back), but its keys and values are random numbers rather than
 the result of a prefill; weights are random too ("data": "synthetic").  Every decode step reads all weights
@@ -82,11 +85,13 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (sizes unchanged)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="do not measure batch 1 and 64")
-    ap.add_argument("--only", choices=["all", "headline", "mixed", "shapes", "timeline", "mma-issue"], default="all",
+    ap.add_argument("--only", choices=["all", "headline", "mixed", "shapes", "timeline", "mma-issue", "zedivik"], default="all",
                     help="headline: the shape's own line only; mixed / shapes: that part only; timeline: the kernels "
                          "of one decode step at --batch as the device ran them (a table on stderr, 4 layers unless "
                          "--layers says otherwise); mma-issue: cycles per tcgen05.mma of one SM for the attention "
-                         "kernel's instruction streams (a table on stderr)")
+                         "kernel's instruction streams (a table on stderr); zedivik: the Zedivik design beside "
+                         "Mistral at equal size (--sizes, --layers, --batch, --prefill-tokens), see measure/compare.py")
+    ap.add_argument("--sizes", default="1b,7b,12b", help="--only zedivik: which sizes of measure/compare.py to run")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -164,6 +169,17 @@ def main(argv=None) -> int:
         print(table, file=sys.stderr)
         rows = [ln.rsplit(None, 4) for ln in table.splitlines()[1:] if ln.strip()]
         print(json.dumps({"impl": "ours", "mma_issue_cycles_each": {r[0].strip(): float(r[3]) for r in rows}}))
+        return 0
+    if args.only == "zedivik":
+        from flambeau_b200.measure import compare
+        with ClockSampler(0) as clocks:
+            time.sleep(0.3)
+            result = compare.run([k for k in args.sizes.split(",") if k], args.layers or 4, args.batch,
+                                 args.prefill_tokens, min(args.steps, 64), args.warmup, pk, gen, say)
+        print(json.dumps({"impl": "ours", "metric": "Zedivik beside Mistral at equal size: decode and prefill tok/s, "
+                          "per-kernel microseconds per layer", "dtype": "bf16", "data": "synthetic", "peak": tag,
+                          "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
+                          "compare": result, "clocks": clocks.summary()}))
         return 0
     if args.only == "timeline":
         layers = args.layers or 4
