@@ -8,7 +8,7 @@
 //
 // Two arrangements of one kernel:
 //   portions  (rows of the sequence > short_rows): a CTA owns 64 rows (4 warps per map), walks the 64-key tiles its
-//             rows can see, every warp scoring the whole tile for its 16 rows, and ends with the epilogue
+//             rows can see, every warp scoring the whole tile for its 16 rows (32 keys at a time), and ends with the epilogue
 //             (a1 - lambda a2, head norm, gate) through shared memory.
 //   split     (rows <= 16: decoded tokens and portions of a few tokens): a CTA owns the 16 rows of (sequence, g) and
 //             a stretch of the key tiles; its 4 warps per map take 16 keys of each tile each and never meet: every
@@ -52,16 +52,33 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// ldmatrix from a 32-bit shared-memory address (base + byte offset), so that the address is one integer add
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
 __device__ __forceinline__ size_t part_index(const DiffArgs& a, int slot, int seq, int g, int row, int map) {
     return ((((size_t)slot * a.n_seqs + seq) * a.nkv + g) * 16 + row) * 2 + map;
 }
 
-template <int KSTEPS, int VTILES, bool SPLIT>
-__global__ void __launch_bounds__(256)
+// Portions: a warp takes a tile's 64 keys in two halves of 32 and fetches its Q fragments from shared memory as it
+// goes, so that (up to value sizes of 128) a thread stays within 128 registers and two CTAs share a multiprocessor:
+// with one, its eight warps leave the tensor pipe idle two cycles in three while they wait on each other's results.
+// EXACT: the key size is KSTEPS * 16 and the value size VTILES * 8, known to the compiler: strides and offsets into
+// shared memory are then constants and the guards of the size loops fall away (the common sizes are built that way;
+// every other multiple of 16 runs the same code with the sizes as arguments).
+template <int KSTEPS, int VTILES, bool SPLIT, bool EXACT>
+__global__ void __launch_bounds__(256, VTILES <= 16 ? 2 : 1)
 diff_attention_mma_kernel(const DiffArgs a) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
-    constexpr int NT = SPLIT ? 2 : 8;              // 8-key n-tiles of a key tile that one warp scores
+    constexpr int HALVES = SPLIT ? 1 : 2;
+    constexpr int NT = SPLIT ? 2 : 4;              // 8-key n-tiles that one warp scores at a time
     constexpr int QROWS = SPLIT ? 16 : 64;
     const int seq = blockIdx.z, g = blockIdx.y;
     const int HG = a.nh / a.nkv;
@@ -72,7 +89,7 @@ diff_attention_mma_kernel(const DiffArgs a) {
     if (R0 >= rows_total) return;
     const int R1 = min(R0 + QROWS, rows_total) - 1;
     const int q_start = a.seq_q_start[seq], pos_start = a.seq_pos_start[seq];
-    const int kd = a.kd, vd = a.vd, W = a.window;
+    const int kd = EXACT ? KSTEPS * 16 : a.kd, vd = EXACT ? VTILES * 8 : a.vd, W = a.window;
     const int p_first = pos_start + R0 / HG, p_last = pos_start + R1 / HG;
     const int t_lo = (W > 0 && p_first - W + 1 > 0) ? p_first - W + 1 : 0, t_hi = p_last;
     int tile_first = t_lo / KT, tile_last = t_hi / KT;
@@ -163,11 +180,17 @@ diff_attention_mma_kernel(const DiffArgs a) {
         row_lo[i] = (W > 0 && row_p[i] - W + 1 > 0) ? row_p[i] - W + 1 : 0;
     }
 
-    uint32_t qf[KSTEPS][4];
+    // byte addresses in shared memory of what this lane hands to ldmatrix: its row of Q, of a K tile (row = key,
+    // plain) and of a V tile (row = key, transposed), each at the lane's 8-column block
+    const uint32_t q_frag = smem_addr(Qs) + 2u * (uint32_t)((map * QROWS + row_tile * 16 + (lane & 15)) * KDP + (lane >> 4) * 8);
+    const uint32_t k_lane = smem_addr(Ks) + 2u * (uint32_t)(((lane >> 4) * 8 + (lane & 7)) * KP + map * kd + ((lane >> 3) & 1) * 8);
+    const uint32_t v_lane = smem_addr(Vs) + 2u * (uint32_t)((((lane >> 3) & 1) * 8 + (lane & 7)) * VP + (lane >> 4) * 8);
+    uint32_t qf[SPLIT ? KSTEPS : 1][4];            // the split arrangement keeps its Q fragments in registers
+    if (SPLIT) {
 #pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks)
-        if (ks * 16 < kd)
-            ldmatrix_x4(qf[ks], Qs + ((size_t)map * QROWS + row_tile * 16 + (lane & 15)) * KDP + ks * 16 + (lane >> 4) * 8);
+        for (int ks = 0; ks < KSTEPS; ++ks)
+            if (ks * 16 < kd) ldsm_x4(qf[SPLIT ? ks : 0], q_frag + ks * 32);
+    }
 
     float o[VTILES][4];
 #pragma unroll
@@ -188,8 +211,12 @@ diff_attention_mma_kernel(const DiffArgs a) {
         __syncthreads();                                                   // ... for all threads, and tile kt-1 is done with
         if (kt + NS - 1 <= tile_last) load_tile((it + NS - 1) % NS, kt + NS - 1);
         cp_async_commit();
-        const __nv_bfloat16* Kt = Ks + (size_t)stage * KT * KP;
-        const __nv_bfloat16* Vt = Vs + (size_t)stage * KT * VP;
+        const uint32_t k_tile = k_lane + 2u * (uint32_t)(stage * KT * KP);
+        const uint32_t v_tile = v_lane + 2u * (uint32_t)(stage * KT * VP);
+
+#pragma unroll 1
+        for (int hf = 0; hf < HALVES; ++hf) {
+        const int koh = koff + hf * (NT * 8);              // the keys of the tile this pass takes
 
         // S = Q K^T for the warp's rows, map and keys
         float s[NT][4];
@@ -198,19 +225,20 @@ diff_attention_mma_kernel(const DiffArgs a) {
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             if (ks * 16 < kd) {
+                if (!SPLIT) ldsm_x4(qf[0], q_frag + ks * 32);
+                const uint32_t (&qa)[4] = qf[SPLIT ? ks : 0];
 #pragma unroll
                 for (int np = 0; np < NT / 2; ++np) {
                     uint32_t kb[4];
-                    ldmatrix_x4(kb, Kt + (size_t)(koff + np * 16 + (lane >> 4) * 8 + (lane & 7)) * KP + map * kd + ks * 16 +
-                                        ((lane >> 3) & 1) * 8);
-                    mma_bf16(s[2 * np], qf[ks], kb[0], kb[1]);
-                    mma_bf16(s[2 * np + 1], qf[ks], kb[2], kb[3]);
+                    ldsm_x4(kb, k_tile + 2u * (uint32_t)((koh + np * 16) * KP + ks * 16));
+                    mma_bf16(s[2 * np], qa, kb[0], kb[1]);
+                    mma_bf16(s[2 * np + 1], qa, kb[2], kb[3]);
                 }
             }
         }
         // scale (to base-2 units), mask, row maxima
         float tmax[2] = {-INFINITY, -INFINITY};
-        const int key0 = kt * KT + koff;
+        const int key0 = kt * KT + koh;
         // (scores stay as the product left them; the scale, positive, enters with the exponent below)
         if (warp_full && key0 + NT * 8 - 1 <= warp_p_min && key0 >= warp_lo_max) {
 #pragma unroll
@@ -269,17 +297,14 @@ diff_attention_mma_kernel(const DiffArgs a) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float p0 = s[2 * kk + (j >> 1)][(j & 1) * 2], p1 = s[2 * kk + (j >> 1)][(j & 1) * 2 + 1];
-                const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
-                __nv_bfloat162 hv; hv.x = h0; hv.y = h1;
-                ah[j] = *reinterpret_cast<uint32_t*>(&hv);
-                al[j] = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
+                ah[j] = pack_bf16(p0, p1);                 // p0 in the low half, p1 in the high half
+                al[j] = pack_bf16(p0 - __uint_as_float(ah[j] << 16), p1 - __uint_as_float(ah[j] & 0xffff0000u));
             }
 #pragma unroll
             for (int vp = 0; vp < VTILES / 2; ++vp) {
                 if (vp * 16 < vd) {
                     uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, Vt + (size_t)(koff + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VP + vp * 16 +
-                                              (lane >> 4) * 8);
+                    ldsm_x4_trans(vb, v_tile + 2u * (uint32_t)((koh + kk * 16) * VP + vp * 16));
                     mma_bf16(o[2 * vp], ah, vb[0], vb[1]);
                     mma_bf16(o[2 * vp], al, vb[0], vb[1]);
                     mma_bf16(o[2 * vp + 1], ah, vb[2], vb[3]);
@@ -287,6 +312,7 @@ diff_attention_mma_kernel(const DiffArgs a) {
                 }
             }
         }
+        }                                                  // the tile's next half
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -437,14 +463,17 @@ size_t smem_bytes(int kd, int vd, bool split, int stages) {
 // Three tiles in shared memory where they fit (two in flight while one is used), else two.  The split arrangement
 // streams the cache and keeps three only while two CTAs still fit on a multiprocessor.
 int stages_for(int kd, int vd, bool split) {
+    const size_t half = SMEM_LIMIT / 2 + 8 * 1024;                  // two CTAs of this size fit on a multiprocessor
     const size_t three = smem_bytes(kd, vd, split, 3);
-    return three <= (split ? SMEM_LIMIT / 2 + 8 * 1024 : SMEM_LIMIT) ? 3 : 2;
+    if (three <= half) return 3;
+    if (smem_bytes(kd, vd, split, 2) <= half && vd <= 128) return 2;   // (larger values: one CTA by registers anyway)
+    return three <= SMEM_LIMIT ? 3 : 2;
 }
 
-template <int KSTEPS, int VTILES, bool SPLIT>
+template <int KSTEPS, int VTILES, bool SPLIT, bool EXACT>
 int launch_diff_mma(const DiffArgs& a, dim3 grid, cudaStream_t stream, int* resident) {
     const size_t smem = smem_bytes(a.kd, a.vd, SPLIT, a.n_stages);
-    auto kern = diff_attention_mma_kernel<KSTEPS, VTILES, SPLIT>;
+    auto kern = diff_attention_mma_kernel<KSTEPS, VTILES, SPLIT, EXACT>;
     static bool raised[FB_MAX_DEVICES] = {};
     if (fb_needs_setup(raised)) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
@@ -464,7 +493,15 @@ int launch_diff_mma(const DiffArgs& a, dim3 grid, cudaStream_t stream, int* resi
 
 template <bool SPLIT>
 int dispatch_diff_mma(const DiffArgs& a, dim3 grid, cudaStream_t stream, int* resident = nullptr) {
-#define FB_DIFF_MMA(KS, VT) return launch_diff_mma<KS, VT, SPLIT>(a, grid, stream, resident)
+#define FB_DIFF_MMA(KS, VT) return launch_diff_mma<KS, VT, SPLIT, false>(a, grid, stream, resident)
+#define FB_DIFF_MMA_EXACT(KS, VT) \
+    if (a.kd == KS * 16 && a.vd == VT * 8) return launch_diff_mma<KS, VT, SPLIT, true>(a, grid, stream, resident)
+    FB_DIFF_MMA_EXACT(4, 16);           // key size 64 per map, value size 128
+    FB_DIFF_MMA_EXACT(3, 12);           // 48 / 96
+    FB_DIFF_MMA_EXACT(2, 8);            // 32 / 64
+    FB_DIFF_MMA_EXACT(4, 8);            // 64 / 64
+    FB_DIFF_MMA_EXACT(8, 16);           // 128 / 128
+#undef FB_DIFF_MMA_EXACT
     if (a.kd <= 64) {
         if (a.vd <= 64) FB_DIFF_MMA(4, 8);
         if (a.vd <= 128) FB_DIFF_MMA(4, 16);
