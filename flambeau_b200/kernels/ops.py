@@ -609,8 +609,12 @@ def diff_attention(ctx, q, out, gate, cache, nh: int, nkv: int, kd: int, vd: int
     if diff_attention_mma_supported(q, nh, nkv, kd, vd) and scale > 0.0 and _DIFF_MMA[0]:
         G = nh // nkv
         short = [ql * G <= 16 for ql in b.seq_q_len]
+        # A step of single tokens may be replayed from a CUDA graph at any context length: its split of the keys
+        # (and the scratch that goes with it) is sized by the longest context the engine allows, in the eager run
+        # as in the captured one, so that both take the same memory.
+        longest = ctx.engine.max_seq_len if b.max_q_len == 1 else b.max_kv_len
         diff_attention_mma(q, out, gate, cache, b.seq_q_start_d, b.seq_q_len_d, b.seq_pos_start_d, b.n_seqs,
-                           b.max_q_len, b.max_kv_len, any(short), not all(short), nh, nkv, kd, vd, window, scale, lam,
+                           b.max_q_len, longest, any(short), not all(short), nh, nkv, kd, vd, window, scale, lam,
                            eps, out_scale, ctx.runtime.status,
                            alloc=lambda n: ctx.ws.alloc((n,), torch.float32))
     else:

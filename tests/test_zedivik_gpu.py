@@ -115,7 +115,9 @@ def test_projection_rows_reach_q_cache_and_gate(dtype):
 # (heads, kv heads, key size per map, value size, window, page size)
 GEOMETRIES = [(4, 2, 16, 48, 20, 16), (6, 1, 16, 32, 33, 16), (8, 2, 48, 64, 100, 16), (2, 1, 64, 128, 40, 8),
               (20, 1, 16, 16, 12, 16), (4, 1, 32, 80, 0, 16), (2, 2, 128, 256, 64, 32), (3, 3, 8, 20, 5, 16),
-              (1, 1, 16, 16, 1, 16)]
+              (1, 1, 16, 16, 1, 16),
+              # the head sizes that the tensor-core kernel is also built for with its sizes known to the compiler
+              (6, 3, 48, 96, 50, 16), (4, 4, 32, 64, 70, 16), (2, 1, 64, 64, 0, 64), (4, 2, 128, 128, 31, 16)]
 # (tokens in the cache, new tokens): first tokens, decoded tokens far into a request and at page borders, portions
 # that start in mid-page beyond the window, portions of two tokens
 SEQS = [(0, 1), (0, 37), (150, 1), (63, 2), (130, 70), (17, 3), (95, 1), (64, 1), (15, 1), (16, 1), (31, 130)]
@@ -178,6 +180,7 @@ def run(case, schedule, tmp_path, cuda_graphs=True):
         dtype=case["dtype"], cache_tokens=tokens, max_requests=4, max_step_tokens=max(tokens, 128),
         max_seq_len=max(tokens, 192), cuda_graphs=cuda_graphs))
     replay(engine, schedule.lines(), tmp_path)
+    run.last_engine = engine
     engine.cache.check_invariants()
     assert not engine.cache.requests, "requests left live after the trace"
     assert all(g.pool.n_free == g.pool.n_pages for g in engine.cache.groups), "pages lost"
@@ -217,6 +220,7 @@ def test_every_token_decoded_from_the_first(case, tmp_path):
         s.add([(rid, [t], [0], p)], end=[rid] if p == len(toks) - 1 else [])
     one = dict(case, requests={rid: toks}, want={rid: case["want"][rid]})
     run(one, s, tmp_path)
+    assert run.last_engine.graph_replays > len(toks) // 2, "single-token steps are replayed from a captured graph"
 
 
 def test_no_loop_at_all(tmp_path):
