@@ -368,16 +368,15 @@ norm_add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ del
     float* xr = x + (size_t)r * H;
     const float* dr = delta + (size_t)r * H;
     const int nvec = H >> 2;
-    float4 v[VPT], d[VPT], wdv[VPT];
+    float4 v[VPT], d[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
         if (c < nvec) {
             v[i] = Vec4<float>::load(xr + 4 * c);
             d[i] = Vec4<float>::load(dr + 4 * c);
-            wdv[i] = Vec4<TWD>::load(wd + 4 * c);
         } else {
-            v[i] = d[i] = wdv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            v[i] = d[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     for (int p = 1; p < n_partials; ++p) {
@@ -400,10 +399,11 @@ norm_add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ del
     for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
         if (c < nvec) {
-            v[i].x += d[i].x * inv_d * (wdv[i].x + wd_offset);
-            v[i].y += d[i].y * inv_d * (wdv[i].y + wd_offset);
-            v[i].z += d[i].z * inv_d * (wdv[i].z + wd_offset);
-            v[i].w += d[i].w * inv_d * (wdv[i].w + wd_offset);
+            const float4 wdv = Vec4<TWD>::load(wd + 4 * c);
+            v[i].x += d[i].x * inv_d * (wdv.x + wd_offset);
+            v[i].y += d[i].y * inv_d * (wdv.y + wd_offset);
+            v[i].z += d[i].z * inv_d * (wdv.z + wd_offset);
+            v[i].w += d[i].w * inv_d * (wdv.w + wd_offset);
             if (!rows) Vec4<float>::store(xr + 4 * c, v[i]);
         }
         ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
@@ -438,7 +438,7 @@ FB_API int fb_norm_add_rmsnorm(float* x, const float* delta, int n_partials, lon
     if (aligned) {
         // hundreds of rows: about 256 threads a row with several vectors each; a few rows: as many threads as vectors
         const int nvec = H / 4;
-        const int want = n_out >= 128 ? (nvec + 255) / 256 : (nvec + 1023) / 1024;
+        const int want = n_out >= 128 ? (nvec + 319) / 320 : (nvec + 1023) / 1024;
         const int vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : want <= 8 ? 8 : 16;
         const int threads_v = (((nvec + vpt - 1) / vpt) + 31) / 32 * 32;
 #define FB_NANV_CASE(V)                                                                                            \

@@ -96,3 +96,15 @@ def test_plain_implementation_is_causal_and_loops(tmp_path):
     assert torch.allclose(pz.forward(cfg, w, toks[:7]), full[:7], atol=1e-12)
     once = dict(cfg, loop=dict(cfg["loop"], times=1))
     assert not torch.allclose(pz.forward(once, w, toks), full, atol=1e-6)
+
+
+def test_command_line_writes_and_inspects_a_model(tmp_path, capsys):
+    from flambeau_b200.cli import main
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(zt.CONFIG_ZC))
+    assert main(["random-model", "--config", str(cfg_file), "--out", str(tmp_path / "m"), "--seed", "3"]) == 0
+    assert main(["inspect", "--model", str(tmp_path / "m")]) == 0
+    out = capsys.readouterr().out
+    assert '"architecture": "Zedivik"' in out and "l1.mix.lq2" in out and "final.norm" in out
+    cfg, w = pz.read_folder(tmp_path / "m")
+    assert pz.forward(cfg, w, [1, 2, 3]).shape == (3, zt.CONFIG_ZC["vocab"])
