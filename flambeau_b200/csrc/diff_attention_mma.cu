@@ -47,6 +47,12 @@ struct DiffArgs {
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16_to(uint32_t dst, const void* src) {          // dst: a shared-memory address
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void zero16_at(uint32_t dst) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -131,6 +137,7 @@ diff_attention_mma_kernel(const DiffArgs a) {
     // ---- the tile loader: 4 threads per key row ----
     const int* table = a.block_table + (size_t)seq * a.table_stride;
     const int base_page = a.table_base ? a.table_base[seq] : 0;
+    const uint32_t ks_base = smem_addr(Ks), vs_base = smem_addr(Vs);
     auto load_tile = [&](int stage, int kt) {
         const int r = tid >> 2, sub = tid & 3;
         const int t = kt * KT + r;
@@ -148,16 +155,18 @@ diff_attention_mma_kernel(const DiffArgs a) {
                 cache_row = ((size_t)page * a.nkv + g) * a.page_size + slot;
             }
         }
-        __nv_bfloat16* kdst = Ks + ((size_t)stage * KT + r) * KP + sub * 8;
-        __nv_bfloat16* vdst = Vs + ((size_t)stage * KT + r) * VP + sub * 8;
+        uint32_t kdst = ks_base + 2u * (uint32_t)((stage * KT + r) * KP + sub * 8);
+        uint32_t vdst = vs_base + 2u * (uint32_t)((stage * KT + r) * VP + sub * 8);
         if (ok) {
             const __nv_bfloat16* ksrc = a.k_pool + cache_row * (2 * kd) + sub * 8;
             const __nv_bfloat16* vsrc = a.v_pool + cache_row * vd + sub * 8;
-            for (int ch = sub; ch < kd / 4; ch += 4, kdst += 32, ksrc += 32) cp_async16(kdst, ksrc);
-            for (int ch = sub; ch < vd / 8; ch += 4, vdst += 32, vsrc += 32) cp_async16(vdst, vsrc);
+#pragma unroll 4
+            for (int ch = sub; ch < kd / 4; ch += 4, kdst += 64, ksrc += 32) cp_async16_to(kdst, ksrc);
+#pragma unroll 4
+            for (int ch = sub; ch < vd / 8; ch += 4, vdst += 64, vsrc += 32) cp_async16_to(vdst, vsrc);
         } else {
-            for (int ch = sub; ch < kd / 4; ch += 4, kdst += 32) *reinterpret_cast<uint4*>(kdst) = make_uint4(0u, 0u, 0u, 0u);
-            for (int ch = sub; ch < vd / 8; ch += 4, vdst += 32) *reinterpret_cast<uint4*>(vdst) = make_uint4(0u, 0u, 0u, 0u);
+            for (int ch = sub; ch < kd / 4; ch += 4, kdst += 64) zero16_at(kdst);
+            for (int ch = sub; ch < vd / 8; ch += 4, vdst += 64) zero16_at(vdst);
         }
     };
 
@@ -204,15 +213,16 @@ diff_attention_mma_kernel(const DiffArgs a) {
     const int warp_p_min = pos_start + warp_R0 / HG;
     const int warp_lo_max = W > 0 ? max(0, pos_start + min(warp_R0 + 15, rows_total - 1) / HG - W + 1) : 0;
 
+    // the stage of the tile in use and the stage to refill (the one tile kt-1 used), and their byte offsets, kept
+    // as running values: NS is an argument, and a division per tile and thread is not free
+    int stage = 0, refill = NS - 1;
+    const uint32_t k_stage_bytes = 2u * (uint32_t)(KT * KP), v_stage_bytes = 2u * (uint32_t)(KT * VP);
+    uint32_t k_tile = k_lane, v_tile = v_lane;
     for (int kt = tile_first; kt <= tile_last; ++kt) {
-        const int it = kt - tile_first;
-        const int stage = it % NS;
         if (NS == 3) cp_async_wait<1>(); else cp_async_wait<0>();          // tile kt has landed ...
         __syncthreads();                                                   // ... for all threads, and tile kt-1 is done with
-        if (kt + NS - 1 <= tile_last) load_tile((it + NS - 1) % NS, kt + NS - 1);
+        if (kt + NS - 1 <= tile_last) load_tile(refill, kt + NS - 1);
         cp_async_commit();
-        const uint32_t k_tile = k_lane + 2u * (uint32_t)(stage * KT * KP);
-        const uint32_t v_tile = v_lane + 2u * (uint32_t)(stage * KT * VP);
 
 #pragma unroll 1
         for (int hf = 0; hf < HALVES; ++hf) {
@@ -313,6 +323,9 @@ diff_attention_mma_kernel(const DiffArgs a) {
             }
         }
         }                                                  // the tile's next half
+        refill = stage;
+        if (++stage == NS) { stage = 0; k_tile = k_lane; v_tile = v_lane; }
+        else { k_tile += k_stage_bytes; v_tile += v_stage_bytes; }
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
