@@ -7,6 +7,7 @@ scale) arrive as arguments; nothing here knows a model.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -622,9 +623,7 @@ def diff_attention(ctx, q, out, gate, cache, nh: int, nkv: int, kd: int, vd: int
                             out_scale, ctx.runtime.status)
 
 
-import os as _os
-
-_DIFF_MMA = [_os.environ.get("FLAMBEAU_DIFF_ATTN_MMA", "1") != "0"]
+_DIFF_MMA = [os.environ.get("FLAMBEAU_DIFF_ATTN_MMA", "1") != "0"]
 
 
 def set_diff_attention_mma(on: bool) -> None:
