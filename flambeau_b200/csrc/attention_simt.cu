@@ -12,17 +12,21 @@
 // row only needs its position and the block table of its sequence (whose row starts
 // at logical page table_base[sequence], or at page 0 without table_base).  It is the
 // attention of the true 32-bit path and the reference for the faster kernels.
+//
+// Value rows may be narrower or wider than key rows (vd against hd).  With `sinks` (one float32 per query head) the
+// softmax has one more slot whose score is that number as it stands (not scaled) and which carries no value: it
+// enters the running maximum and the denominator once, and nothing else.
 #include "common.cuh"
 
-template <typename T, int NDR>   // NDR = ceil(head_dim / 32) accumulator registers per lane
+template <typename T, int NDR>   // NDR = ceil(value size / 32) accumulator registers per lane
 __global__ void __launch_bounds__(128)
 paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ out, long out_stride,
                             const T* __restrict__ k_pool, const T* __restrict__ v_pool, int page_size,
                             int n_pages, const int* __restrict__ block_table, int table_stride,
                             const int* __restrict__ table_base,
                             const int* __restrict__ positions, const int* __restrict__ row_seq, int n, int nh,
-                            int nkv, int hd, int window, float scale, const float* __restrict__ score_slopes,
-                            int* status) {
+                            int nkv, int hd, int vd, int window, float scale,
+                            const float* __restrict__ score_slopes, const float* __restrict__ sinks, int* status) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     extern __shared__ float q_sh[];                    // [4 warps][hd]
@@ -83,21 +87,29 @@ paged_attention_simt_kernel(const T* __restrict__ q, long q_stride, T* __restric
             const int page_j = __shfl_sync(0xffffffffu, my_page, j);
             if (page_j < 0) continue;
             const int tj = base + j;
-            const T* vr = v_pool + (((size_t)page_j * nkv + kvh) * page_size + (tj % page_size)) * hd;
+            const T* vr = v_pool + (((size_t)page_j * nkv + kvh) * page_size + (tj % page_size)) * vd;
 #pragma unroll
             for (int r = 0; r < NDR; ++r) {
                 const int d = lane + 32 * r;
-                if (d < hd) acc[r] = fmaf(pj, fb_to_float(vr[d]), acc[r]);
+                if (d < vd) acc[r] = fmaf(pj, fb_to_float(vr[d]), acc[r]);
             }
         }
         m = m_new;
     }
+    if (sinks) {                                        // the slot without key and value
+        const float sk = sinks[head];
+        const float m_new = fmaxf(m, sk);
+        const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int r = 0; r < NDR; ++r) acc[r] *= corr;
+    }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    T* op = out + (size_t)row * out_stride + (size_t)head * hd;
+    T* op = out + (size_t)row * out_stride + (size_t)head * vd;
 #pragma unroll
     for (int r = 0; r < NDR; ++r) {
         const int d = lane + 32 * r;
-        if (d < hd) op[d] = fb_from_float<T>(acc[r] * inv);
+        if (d < vd) op[d] = fb_from_float<T>(acc[r] * inv);
     }
 }
 
@@ -106,13 +118,14 @@ static int launch_attention_simt(const void* q, long q_stride, void* out, long o
                                  const void* v_pool, int page_size, int n_pages, const int* block_table,
                                  int table_stride, const int* table_base, const int* positions, const int* row_seq,
                                  int n, int nh,
-                                 int nkv, int hd, int window, float scale, const float* score_slopes, int* status,
-                                 cudaStream_t stream) {
+                                 int nkv, int hd, int vd, int window, float scale, const float* score_slopes,
+                                 const float* sinks, int* status, cudaStream_t stream) {
     const long items = (long)n * nh;
     const unsigned blocks = (unsigned)((items + 3) / 4);
     fb_launch((paged_attention_simt_kernel<T, NDR>), blocks, 128, 4 * hd * sizeof(float), stream, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, page_size, n_pages,
-        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, window, scale, score_slopes, status);
+        block_table, table_stride, table_base, positions, row_seq, n, nh, nkv, hd, vd, window, scale, score_slopes, sinks,
+        status);
     return fb_check_launch("paged_attention_simt");
 }
 
@@ -120,21 +133,22 @@ FB_API int fb_paged_attention_simt(const void* q, long long q_stride, void* out,
                                    const void* k_pool, const void* v_pool, int page_size, int n_pages,
                                    const int* block_table, int table_stride, const int* table_base,
                                    const int* positions, const int* row_seq, int n, int nh, int nkv, int hd,
-                                   int window, float scale, const float* score_slopes, int* status,
-                                   cudaStream_t stream) {
+                                   int vd, int window, float scale, const float* score_slopes, const float* sinks,
+                                   int* status, cudaStream_t stream) {
+    if (vd <= 0) vd = hd;
     FB_REQUIRE(n >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention: bad sizes n=%d heads=%d kv=%d hd=%d", n, nh, nkv, hd);
     FB_REQUIRE(nh % nkv == 0, "attention: %d query heads are not a multiple of %d key/value heads", nh, nkv);
-    FB_REQUIRE(hd <= 512, "attention: head size %d is larger than 512", hd);
+    FB_REQUIRE(hd <= 512 && vd <= 512, "attention: head size %d / value size %d is larger than 512", hd, vd);
     FB_REQUIRE(page_size > 0 && n_pages > 0 && window >= 0, "attention: bad cache geometry");
     if (n == 0) return 0;
 #define FB_ATTN_CASE(NDR)                                                                                      \
     FB_DISPATCH_DTYPE(dtype, T, return (launch_attention_simt<T, NDR>(q, (long)q_stride, out, (long)out_stride,     \
         k_pool, v_pool, page_size, n_pages, block_table, table_stride, table_base, positions, row_seq, n, nh, \
-        nkv, hd, window, scale, score_slopes, status, stream)))
-    if (hd <= 32) { FB_ATTN_CASE(1); }
-    else if (hd <= 64) { FB_ATTN_CASE(2); }
-    else if (hd <= 128) { FB_ATTN_CASE(4); }
-    else if (hd <= 256) { FB_ATTN_CASE(8); }
+        nkv, hd, vd, window, scale, score_slopes, sinks, status, stream)))
+    if (vd <= 32) { FB_ATTN_CASE(1); }
+    else if (vd <= 64) { FB_ATTN_CASE(2); }
+    else if (vd <= 128) { FB_ATTN_CASE(4); }
+    else if (vd <= 256) { FB_ATTN_CASE(8); }
     else { FB_ATTN_CASE(16); }
 #undef FB_ATTN_CASE
     return 0;

@@ -60,6 +60,17 @@ __device__ __forceinline__ float fb_gate_times(int act, float g, float u) {
     return g / (1.0f + expf(-g)) * u;             // SiLU (crates/model-ops/src/ops/activation.rs:107-118)
 }
 
+// ---- activations that stand alone ---------------------------------------------
+// out = act(z) for feed-forwards without a gate.  0 leaves z as it is.
+enum FbPlainAct : int { FB_PLAIN_NONE = 0, FB_PLAIN_SILU = 1, FB_PLAIN_GELU_TANH = 2, FB_PLAIN_RELU_SQUARED = 3 };
+inline bool fb_plain_act_known(int act) { return act >= FB_PLAIN_NONE && act <= FB_PLAIN_RELU_SQUARED; }
+__device__ __forceinline__ float fb_plain_act(int act, float z) {
+    if (act == FB_PLAIN_RELU_SQUARED) { const float r = fmaxf(z, 0.0f); return r * r; }
+    if (act == FB_PLAIN_SILU) return z / (1.0f + expf(-z));
+    if (act == FB_PLAIN_GELU_TANH) return fb_gate_times(FB_ACT_GELU_TANH, z, 1.0f);
+    return z;
+}
+
 // ---- launches ---------------------------------------------------------------
 // Kernels of a step run back to back on one stream.  With programmatic dependent launch the next kernel of the
 // stream may be scheduled while this one is still draining: every kernel begins with fb_pdl_launch_dependents()

@@ -833,3 +833,140 @@ FB_API int fb_gate_mul(const void* gate_up, long long stride, int in_dtype, int 
             (const TI*)gate_up, stride, n_partials, (long)partial_stride, (T*)out, n, I, act))));
     return fb_check_launch("gate_mul");
 }
+
+// ---------------------------------------------------------------------------
+// act(z) for a feed-forward without a gate: out[r, c] = act(sum of the shares of z[r, c]), act an FbPlainAct code.
+// ---------------------------------------------------------------------------
+template <typename TI, typename T>
+__global__ void activation_kernel(const TI* __restrict__ z, long stride, int n_partials, long partial_stride,
+                                  T* __restrict__ out, int n, int I, int act) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * I) return;
+    const int r = (int)(idx / I), c = (int)(idx - (size_t)r * I);
+    out[idx] = fb_from_float<T>(fb_plain_act(act, slab_sum(z + (size_t)r * stride, c, n_partials, partial_stride)));
+}
+
+FB_API int fb_activation(const void* z, long long stride, int in_dtype, int n_partials, long long partial_stride,
+                         void* out, int out_dtype, int n, int I, int act, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && I > 0 && stride >= I, "activation: bad sizes n=%d I=%d stride=%lld", n, I, stride);
+    FB_REQUIRE(fb_plain_act_known(act), "activation: unknown activation code %d", act);
+    if (n == 0) return 0;
+    if (n_partials < 1) n_partials = 1;
+    const size_t total = (size_t)n * I;
+    FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
+        (fb_launch((activation_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,
+            (const TI*)z, (long)stride, n_partials, (long)partial_stride, (T*)out, n, I, act))));
+    return fb_check_launch("activation");
+}
+
+// ---------------------------------------------------------------------------
+// x[r, :] += v[:] for the first n rows of the float32 stream (a learned vector that joins every token alike).
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void add_row_kernel(float* __restrict__ x, const TW* __restrict__ v, int n, int H) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * H) return;
+    x[idx] += fb_to_float(v[idx % H]);
+}
+
+FB_API int fb_add_row(float* x, const void* v, int v_dtype, int n, int H, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && H > 0, "add_row: bad sizes");
+    if (n == 0) return 0;
+    const size_t total = (size_t)n * H;
+    FB_DISPATCH_DTYPE(v_dtype, TW,
+        (fb_launch((add_row_kernel<TW>), (unsigned)((total + 255) / 256), 256, 0, stream, x, (const TW*)v, n, H)));
+    return fb_check_launch("add_row");
+}
+
+// ---------------------------------------------------------------------------
+// Mixers that run side by side on one input: out[r] = sum_b coef_b * rmsnorm(y_b[r]) * w_b, every branch's output y_b
+// (float32, possibly split-K shares) normalised over the width with a weight and a factor of its own.  One CTA a row,
+// two walks over the shares: sums of squares, then the mix.
+// ---------------------------------------------------------------------------
+constexpr int FB_MAX_BRANCHES = 4;
+struct FbBranches {
+    const float* y[FB_MAX_BRANCHES];
+    int n_partials[FB_MAX_BRANCHES];
+    long partial_stride[FB_MAX_BRANCHES];
+    const void* weight[FB_MAX_BRANCHES];
+    float coef[FB_MAX_BRANCHES];
+    int count;
+};
+
+template <typename TW>
+__global__ void __launch_bounds__(256)
+branch_norm_mix_kernel(FbBranches b, float eps, float weight_offset, float* __restrict__ out, int H) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    __shared__ float red[32];
+    __shared__ float inv[FB_MAX_BRANCHES];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    for (int i = 0; i < b.count; ++i) {
+        const float* y = b.y[i] + (size_t)row * H;
+        float s = 0.0f;
+        for (int c = tid; c < H; c += blockDim.x) {
+            const float v = slab_sum(y, c, b.n_partials[i], b.partial_stride[i]);
+            s = fmaf(v, v, s);
+        }
+        s = fb_block_sum(s, red);
+        if (tid == 0) inv[i] = b.coef[i] / sqrtf(s / (float)H + eps);
+    }
+    __syncthreads();
+    for (int c = tid; c < H; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int i = 0; i < b.count; ++i) {
+            const float v = slab_sum(b.y[i] + (size_t)row * H, c, b.n_partials[i], b.partial_stride[i]);
+            acc = fmaf(v * inv[i], fb_to_float(((const TW*)b.weight[i])[c]) + weight_offset, acc);
+        }
+        out[(size_t)row * H + c] = acc;
+    }
+}
+
+FB_API int fb_branch_norm_mix(int count, const float* const* y, const int* n_partials, const long long* partial_stride,
+                              const void* const* weight, int w_dtype, const float* coef, float eps, float weight_offset,
+                              float* out, int n, int H, cudaStream_t stream) {
+    FB_REQUIRE(count >= 1 && count <= FB_MAX_BRANCHES, "branch_norm_mix: %d branches (1 to %d)", count, FB_MAX_BRANCHES);
+    FB_REQUIRE(n >= 0 && H > 0, "branch_norm_mix: bad sizes");
+    if (n == 0) return 0;
+    FbBranches b = {};
+    b.count = count;
+    for (int i = 0; i < count; ++i) {
+        b.y[i] = y[i];
+        b.n_partials[i] = n_partials[i] < 1 ? 1 : n_partials[i];
+        b.partial_stride[i] = (long)partial_stride[i];
+        b.weight[i] = weight[i];
+        b.coef[i] = coef[i];
+    }
+    FB_DISPATCH_DTYPE(w_dtype, TW,
+        (fb_launch((branch_norm_mix_kernel<TW>), dim3(n), dim3(256), 0, stream, b, eps, weight_offset, out, H)));
+    return fb_check_launch("branch_norm_mix");
+}
+
+// ---------------------------------------------------------------------------
+// x[r, c] += sum of the shares of delta[r, c]: a part's pending output joins the float32 stream without a norm
+// behind it (for a part that wants the whole stream rather than a normalised copy of it).
+// ---------------------------------------------------------------------------
+__global__ void add_slabs_kernel(float* __restrict__ x, const float* __restrict__ delta, int n_partials,
+                                 long partial_stride, size_t total) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    float v = delta[idx];
+    for (int p = 1; p < n_partials; ++p) v += delta[(size_t)p * partial_stride + idx];
+    x[idx] += v;
+}
+
+FB_API int fb_add_slabs(float* x, const float* delta, int n_partials, long long partial_stride, int n, int H,
+                        cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && H > 0, "add_slabs: bad sizes");
+    if (n == 0) return 0;
+    const size_t total = (size_t)n * H;
+    fb_launch(add_slabs_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, delta,
+              n_partials < 1 ? 1 : n_partials, (long)partial_stride, total);
+    return fb_check_launch("add_slabs");
+}

@@ -1,0 +1,276 @@
+// The gated delta rule: a linear recurrence with one matrix of state per head, S [dk, dv] in float32, which a token
+// first lets decay, then corrects along its key towards its value, then reads with its query:
+//
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q        (g, beta: one number per head and token)
+//
+// Every column of S (one value dimension) goes through this on its own, so columns are spread over threads and a
+// request's tokens are taken in order; nothing but q, k, g and beta is shared between columns.
+//
+// Kernels, in the order a step runs them:
+//   gdr_prepare      per token: add the projection's split-K shares, the short causal convolution over time with its
+//                    SiLU on the q, k and v channels (inputs before the portion's start come from the request's
+//                    kept tail), q and k made unit vectors per head (q also times `q_scale`), beta = sigmoid,
+//                    g = exp(-exp(A_log) * softplus(a + dt_bias)); all float32
+//   gdr_conv_tail    per request: the last taps-1 convolution inputs of the step become the kept tail
+//   gdr_recurrent    per (request, head, slice of columns): the recurrence over the step's tokens, state in registers
+//   gdr_out_norm     per (token, head): o / rms(o) * weight * silu(gate), rounded to the engine's dtype
+//
+// A request's slot of state is one float32 array: S as [heads][dk][dv], then the tail as [taps-1][channels]
+// (oldest first).  Projection rows are [q: G*dk | k: G*dk | v: H*dv | b: H | a: H | gate: H*dv]; head h of H reads
+// q/k head h / (H / G).
+#include "common.cuh"
+
+__device__ __forceinline__ float gdr_slab_sum(const float* row, int c, int n_partials, long partial_stride) {
+    float v = row[c];
+    for (int p = 1; p < n_partials; ++p) v += row[(size_t)p * partial_stride + c];
+    return v;
+}
+__device__ __forceinline__ float gdr_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gdr_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+template <typename TW>
+__global__ void __launch_bounds__(256)
+gdr_prepare_kernel(const float* __restrict__ proj, long proj_stride, int n_partials, long partial_stride,
+                   const TW* __restrict__ conv_w, int taps, const TW* __restrict__ a_log, const TW* __restrict__ dt_bias,
+                   const float* __restrict__ state, long state_stride, long tail_off, const int* __restrict__ row_seq,
+                   const int* __restrict__ seq_q_start, const int* __restrict__ seq_slot, float* __restrict__ qkv,
+                   float* __restrict__ beta, float* __restrict__ decay, int G, int H, int dk, int dv, float q_scale,
+                   float unit_eps) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    extern __shared__ float sh[];                      // [2 * G * dk] q and k channels after convolution and SiLU
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const int qk = G * dk, C = 2 * qk + H * dv;
+    const int seq = row_seq[row];
+    const int i = row - seq_q_start[seq];              // place within the step's portion of this request
+    const float* tail = state + (size_t)seq_slot[seq] * state_stride + tail_off;
+    float* out = qkv + (size_t)row * C;
+    for (int c = tid; c < C; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = i - (taps - 1 - j);
+            const float x = src >= 0
+                ? gdr_slab_sum(proj + (size_t)(row - (taps - 1 - j)) * proj_stride, c, n_partials, partial_stride)
+                : tail[(size_t)(taps - 1 + src) * C + c];
+            acc = fmaf(fb_to_float(conv_w[(size_t)c * taps + j]), x, acc);
+        }
+        const float y = gdr_silu(acc);
+        if (c < 2 * qk) sh[c] = y; else out[c] = y;
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < 2 * G; h += nwarps) {       // q heads, then k heads
+        const float* x = sh + (size_t)h * dk;
+        float s = 0.0f;
+        for (int d = lane; d < dk; d += 32) s = fmaf(x[d], x[d], s);
+        s = fb_warp_sum(s);
+        const float f = (h < G ? q_scale : 1.0f) / sqrtf(s + unit_eps);
+        for (int d = lane; d < dk; d += 32) out[(size_t)h * dk + d] = x[d] * f;
+    }
+    const float* pr = proj + (size_t)row * proj_stride;
+    for (int h = tid; h < H; h += blockDim.x) {
+        const float b = gdr_slab_sum(pr, C + h, n_partials, partial_stride);
+        const float a = gdr_slab_sum(pr, C + H + h, n_partials, partial_stride);
+        beta[(size_t)row * H + h] = 1.0f / (1.0f + expf(-b));
+        decay[(size_t)row * H + h] = expf(-expf(fb_to_float(a_log[h])) * gdr_softplus(a + fb_to_float(dt_bias[h])));
+    }
+}
+
+__global__ void gdr_conv_tail_kernel(const float* __restrict__ proj, long proj_stride, int n_partials, long partial_stride,
+                                     int taps, float* __restrict__ state, long state_stride, long tail_off,
+                                     const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                                     const int* __restrict__ seq_slot, int C) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int seq = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int L = seq_q_len[seq], start = seq_q_start[seq];
+    float* tail = state + (size_t)seq_slot[seq] * state_stride + tail_off;
+    // ascending m: an entry taken from the old tail lies above the one being written
+    for (int m = 0; m < taps - 1; ++m) {
+        const int src = L - (taps - 1) + m;
+        tail[(size_t)m * C + c] = src >= 0
+            ? gdr_slab_sum(proj + (size_t)(start + src) * proj_stride, c, n_partials, partial_stride)
+            : tail[(size_t)(taps - 1 + src) * C + c];
+    }
+}
+
+// R state values a lane, LPC lanes a column (the key dimension d = lane + LPC * r), 256 / LPC columns a CTA.
+template <int R, int LPC>
+__global__ void __launch_bounds__(256)
+gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
+                     float* __restrict__ state, long state_stride, const int* __restrict__ seq_q_start,
+                     const int* __restrict__ seq_q_len, const int* __restrict__ seq_slot, float* __restrict__ o,
+                     int G, int H, int dk, int dv) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    constexpr int COLS = 256 / LPC, CH = 16;           // columns of this CTA; tokens fetched at a time
+    extern __shared__ float sh[];
+    float* qs = sh;                                    // [CH][dk]
+    float* ks = qs + CH * dk;                          // [CH][dk]
+    float* vs = ks + CH * dk;                          // [CH][COLS]
+    float* bs = vs + CH * COLS;                        // [CH] beta
+    float* gs = bs + CH;                               // [CH] decay
+    const int seq = blockIdx.x / H, head = blockIdx.x - seq * H;
+    const int g = head / (H / G);
+    const int tid = threadIdx.x;
+    const int li = tid % LPC, col = blockIdx.y * COLS + tid / LPC;
+    const bool live = col < dv;
+    const int qk = G * dk, C = 2 * qk + H * dv;
+    const int start = seq_q_start[seq], L = seq_q_len[seq];
+    float* S = state + (size_t)seq_slot[seq] * state_stride + (size_t)head * dk * dv;
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = li + LPC * r;
+        s[r] = (live && d < dk) ? S[(size_t)d * dv + col] : 0.0f;
+    }
+    for (int t0 = 0; t0 < L; t0 += CH) {
+        const int cnt = min(CH, L - t0);
+        __syncthreads();
+        for (int e = tid; e < cnt * dk; e += 256) {
+            const int t = e / dk, d = e - t * dk;
+            const float* rowp = qkv + (size_t)(start + t0 + t) * C;
+            qs[e] = rowp[(size_t)g * dk + d];
+            ks[e] = rowp[qk + (size_t)g * dk + d];
+        }
+        for (int e = tid; e < cnt * COLS; e += 256) {
+            const int t = e / COLS, cc = e - t * COLS, c2 = blockIdx.y * COLS + cc;
+            vs[e] = c2 < dv ? qkv[(size_t)(start + t0 + t) * C + 2 * qk + (size_t)head * dv + c2] : 0.0f;
+        }
+        if (tid < cnt) {
+            bs[tid] = beta[(size_t)(start + t0 + tid) * H + head];
+            gs[tid] = decay[(size_t)(start + t0 + tid) * H + head];
+        }
+        __syncthreads();
+        for (int t = 0; t < cnt; ++t) {
+            const float gt = gs[t], bt = bs[t];
+            const float* kt = ks + t * dk;
+            const float* qt = qs + t * dk;
+            float dot = 0.0f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = li + LPC * r;
+                s[r] *= gt;
+                if (d < dk) dot = fmaf(s[r], kt[d], dot);
+            }
+#pragma unroll
+            for (int off = LPC / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+            const float u = bt * (vs[t * COLS + tid / LPC] - dot);
+            float rd = 0.0f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = li + LPC * r;
+                if (d < dk) {
+                    s[r] = fmaf(kt[d], u, s[r]);
+                    rd = fmaf(s[r], qt[d], rd);
+                }
+            }
+#pragma unroll
+            for (int off = LPC / 2; off > 0; off >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, off);
+            if (live && li == 0) o[(size_t)(start + t0 + t) * H * dv + (size_t)head * dv + col] = rd;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = li + LPC * r;
+        if (live && d < dk) S[(size_t)d * dv + col] = s[r];
+    }
+}
+
+template <typename TW, typename T>
+__global__ void __launch_bounds__(128)
+gdr_out_norm_kernel(const float* __restrict__ o, const float* __restrict__ proj, long proj_stride, int n_partials,
+                    long partial_stride, int gate_off, const TW* __restrict__ weight, float eps, T* __restrict__ out,
+                    int n, int H, int dv) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long item = (long)blockIdx.x * 4 + warp;
+    if (item >= (long)n * H) return;
+    const int row = (int)(item / H), head = (int)(item - (long)row * H);
+    const float* x = o + (size_t)row * H * dv + (size_t)head * dv;
+    float s = 0.0f;
+    for (int d = lane; d < dv; d += 32) s = fmaf(x[d], x[d], s);
+    s = fb_warp_sum(s);
+    const float inv = 1.0f / sqrtf(s / (float)dv + eps);
+    const float* pr = proj + (size_t)row * proj_stride;
+    for (int d = lane; d < dv; d += 32) {
+        const float gate = gdr_slab_sum(pr, gate_off + head * dv + d, n_partials, partial_stride);
+        out[(size_t)row * H * dv + (size_t)head * dv + d] =
+            fb_from_float<T>(x[d] * inv * fb_to_float(weight[d]) * gdr_silu(gate));
+    }
+}
+
+FB_API int fb_gdr_prepare(const float* proj, long long proj_stride, int n_partials, long long partial_stride,
+                          const void* conv_w, int taps, const void* a_log, const void* dt_bias, int w_dtype,
+                          float* state, long long state_stride, long long tail_off, const int* row_seq,
+                          const int* seq_q_start, const int* seq_q_len, const int* seq_slot, int n_seqs, float* qkv,
+                          float* beta, float* decay, int n, int G, int H, int dk, int dv, float q_scale,
+                          float unit_eps, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && G > 0 && H > 0 && H % G == 0 && dk > 0 && dv > 0 && taps >= 1, "gated delta: bad sizes");
+    const long long C = 2LL * G * dk + (long long)H * dv;
+    FB_REQUIRE(proj_stride >= C + 2LL * H + (long long)H * dv, "gated delta: projection rows are too short");
+    if (n == 0) return 0;
+    if (n_partials < 1) n_partials = 1;
+    const size_t smem = (size_t)2 * G * dk * sizeof(float);
+    FB_REQUIRE(smem <= 200 * 1024, "gated delta: q and k of a token (%zu bytes) do not fit shared memory", smem);
+    FB_DISPATCH_DTYPE(w_dtype, TW, {
+        auto kernel = gdr_prepare_kernel<TW>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fb_launch(kernel, dim3(n), dim3(256), smem, stream, proj, (long)proj_stride, n_partials, (long)partial_stride,
+                  (const TW*)conv_w, taps, (const TW*)a_log, (const TW*)dt_bias, (const float*)state, (long)state_stride,
+                  (long)tail_off, row_seq, seq_q_start, seq_slot, qkv, beta, decay, G, H, dk, dv, q_scale, unit_eps);
+    });
+    int rc = fb_check_launch("gdr_prepare");
+    if (rc || taps < 2) return rc;
+    fb_launch(gdr_conv_tail_kernel, dim3(n_seqs, (unsigned)((C + 127) / 128)), dim3(128), 0, stream, proj,
+              (long)proj_stride, n_partials, (long)partial_stride, taps, state, (long)state_stride, (long)tail_off,
+              seq_q_start, seq_q_len, seq_slot, (int)C);
+    return fb_check_launch("gdr_conv_tail");
+}
+
+template <int R, int LPC>
+static int launch_gdr_recurrent(const float* qkv, const float* beta, const float* decay, float* state,
+                                long state_stride, const int* seq_q_start, const int* seq_q_len, const int* seq_slot,
+                                int n_seqs, float* o, int G, int H, int dk, int dv, cudaStream_t stream) {
+    constexpr int COLS = 256 / LPC, CH = 16;
+    const size_t smem = ((size_t)2 * CH * dk + CH * COLS + 2 * CH) * sizeof(float);
+    auto kernel = gdr_recurrent_kernel<R, LPC>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    fb_launch(kernel, dim3(n_seqs * H, (dv + COLS - 1) / COLS), dim3(256), smem, stream, qkv, beta, decay, state,
+              state_stride, seq_q_start, seq_q_len, seq_slot, o, G, H, dk, dv);
+    return fb_check_launch("gdr_recurrent");
+}
+
+FB_API int fb_gdr_recurrent(const float* qkv, const float* beta, const float* decay, float* state,
+                            long long state_stride, const int* seq_q_start, const int* seq_q_len, const int* seq_slot,
+                            int n_seqs, float* o, int G, int H, int dk, int dv, cudaStream_t stream) {
+    FB_REQUIRE(n_seqs >= 0 && G > 0 && H > 0 && H % G == 0 && dk > 0 && dv > 0, "gated delta: bad sizes");
+    FB_REQUIRE(dk <= 1024, "gated delta: key size %d is larger than 1024", dk);
+    if (n_seqs == 0) return 0;
+#define FB_GDR_CASE(R, LPC) return launch_gdr_recurrent<R, LPC>(qkv, beta, decay, state, (long)state_stride, \
+        seq_q_start, seq_q_len, seq_slot, n_seqs, o, G, H, dk, dv, stream)
+    if (dk <= 32) FB_GDR_CASE(8, 4);
+    if (dk <= 64) FB_GDR_CASE(16, 4);
+    if (dk <= 128) FB_GDR_CASE(32, 4);
+    if (dk <= 256) FB_GDR_CASE(32, 8);
+    if (dk <= 512) FB_GDR_CASE(32, 16);
+    FB_GDR_CASE(32, 32);
+#undef FB_GDR_CASE
+}
+
+FB_API int fb_gdr_out_norm(const float* o, const float* proj, long long proj_stride, int n_partials,
+                           long long partial_stride, int gate_off, const void* weight, int w_dtype, float eps,
+                           void* out, int out_dtype, int n, int H, int dv, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && H > 0 && dv > 0, "gated delta: bad sizes");
+    if (n == 0) return 0;
+    if (n_partials < 1) n_partials = 1;
+    const long items = (long)n * H;
+    FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, T,
+        (fb_launch((gdr_out_norm_kernel<TW, T>), dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, o, proj,
+                   (long)proj_stride, n_partials, (long)partial_stride, gate_off, (const TW*)weight, eps, (T*)out, n, H,
+                   dv))));
+    return fb_check_launch("gdr_out_norm");
+}

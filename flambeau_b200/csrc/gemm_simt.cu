@@ -99,3 +99,107 @@ FB_API int fb_gemm_simt(const void* A, int a_dtype, long long lda, const void* W
         return (launch_gemm_simt<TA, TW, TO>(A, (long)lda, W, (long)ldw, out, (long)ldo, M, N, K, stream)))));
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// The grouped form: the rows are cut into tiles of BM, and every tile multiplies with the weights of its own group
+// (an expert): W + tile_group[tile] * group_stride.  A tile whose group is negative is skipped.  Row m of A is row
+// row_index[m] of the caller's matrix (negative: a row of zeros; nullptr: row m itself), so tokens that were
+// sorted by expert need not be copied side by side first.  `act` (an FbPlainAct code) is applied to every output.
+// Each output element still sums its K products in ascending k in one thread.
+// ---------------------------------------------------------------------------
+template <typename TA, typename TW, typename TO, int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_simt_grouped_kernel(const TA* __restrict__ A, long lda, const int* __restrict__ row_index,
+                         const TW* __restrict__ W, long ldw, long group_stride, const int* __restrict__ tile_group,
+                         TO* __restrict__ out, long ldo, int M, int N, int K, int act) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    constexpr int THREADS = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ int src_row[BM];
+    const int group = tile_group[blockIdx.y];
+    if (group < 0) return;
+    const TW* Wg = W + (size_t)group * group_stride;
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    for (int r = tid; r < BM; r += THREADS) {
+        const int m = m0 + r;
+        src_row[r] = m < M ? (row_index ? row_index[m] : m) : -1;
+    }
+    __syncthreads();
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int e = tid; e < BM * BK; e += THREADS) {
+            const int row = e / BK, kk = e - row * BK;
+            const int src = src_row[row], k = k0 + kk;
+            As[kk][row] = (src >= 0 && k < K) ? fb_to_float(A[(size_t)src * lda + k]) : 0.0f;
+        }
+#pragma unroll
+        for (int e = tid; e < BN * BK; e += THREADS) {
+            const int row = e / BK, kk = e - row * BK;
+            const int n = n0 + row, k = k0 + kk;
+            Ws[kk][row] = (n < N && k < K) ? fb_to_float(Wg[(size_t)n * ldw + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n < N) out[(size_t)m * ldo + n] = fb_from_float<TO>(fb_plain_act(act, acc[i][j]));
+        }
+    }
+}
+
+// M = rows of the padded order (a multiple of `tile`); tile_group has M / tile entries.  `tile` is 16 or 64.
+FB_API int fb_gemm_simt_grouped(const void* A, int a_dtype, long long lda, const int* row_index, const void* W,
+                                int w_dtype, long long ldw, long long group_stride, const int* tile_group, int tile,
+                                void* out, int o_dtype, long long ldo, int M, int N, int K, int act,
+                                cudaStream_t stream) {
+    FB_REQUIRE(M >= 0 && N > 0 && K > 0, "grouped gemm: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(tile == 16 || tile == 64, "grouped gemm: row tiles of 16 or 64, not %d", tile);
+    FB_REQUIRE(M % tile == 0 && tile_group, "grouped gemm: the rows must be whole tiles with a group each");
+    FB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "grouped gemm: a row stride is shorter than its row");
+    FB_REQUIRE(fb_plain_act_known(act), "grouped gemm: unknown activation code %d", act);
+    if (M == 0) return 0;
+    FB_REQUIRE(M / tile <= 65535, "grouped gemm: too many row tiles (M=%d)", M);
+    if (tile == 64) {
+        constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+        dim3 grid((N + BN - 1) / BN, M / BM);
+        FB_DISPATCH_DTYPE(a_dtype, TA, FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(o_dtype, TO,
+            (fb_launch((gemm_simt_grouped_kernel<TA, TW, TO, BM, BN, BK, TM, TN>), grid, (BM / TM) * (BN / TN), 0, stream,
+                       (const TA*)A, (long)lda, row_index, (const TW*)W, (long)ldw, (long)group_stride, tile_group,
+                       (TO*)out, (long)ldo, M, N, K, act)))));
+    } else {
+        constexpr int BM = 16, BN = 64, BK = 32, TM = 2, TN = 2;
+        dim3 grid((N + BN - 1) / BN, M / BM);
+        FB_DISPATCH_DTYPE(a_dtype, TA, FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(o_dtype, TO,
+            (fb_launch((gemm_simt_grouped_kernel<TA, TW, TO, BM, BN, BK, TM, TN>), grid, (BM / TM) * (BN / TN), 0, stream,
+                       (const TA*)A, (long)lda, row_index, (const TW*)W, (long)ldw, (long)group_stride, tile_group,
+                       (TO*)out, (long)ldo, M, N, K, act)))));
+    }
+    return fb_check_launch("gemm_simt_grouped");
+}

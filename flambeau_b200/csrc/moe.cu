@@ -1,0 +1,170 @@
+// Routed experts: which experts a token uses, the order that puts every expert's tokens side by side for the
+// grouped products, and the weighted sum that brings the experts' outputs back to the tokens.
+//
+//   moe_route    per token (one warp): router logits z = Wr h + b in float32, the `top` largest (the lower index wins a
+//                tie), their weights = softmax over the chosen logits only; optionally one more number per token,
+//                sigmoid(w_gate . h), for a shared expert
+//   moe_sort     one CTA: (token, choice) pairs counted per expert, every expert's stretch padded to a multiple of
+//                the products' row tile, so that a row tile belongs to one expert; writes for every place of the
+//                padded order its token (-1: padding), for every pair its place, for every row tile its expert
+//                (-1: unused).  Sizes are upper bounds known on the host, so nothing has to come back from the device
+//   moe_combine  per token: sum_k weight_k * expert_out[place of (token, k)] + gate * shared_out
+#include "common.cuh"
+
+constexpr int MOE_MAX_LOGITS_PER_LANE = 16;            // 512 experts at most
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, long h_stride, const TW* __restrict__ wr, const TW* __restrict__ br,
+                 const TW* __restrict__ w_gate, int n, int D, int E, int K, int* __restrict__ chosen,
+                 float* __restrict__ share, float* __restrict__ gate) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= n) return;
+    const T* x = h + (size_t)row * h_stride;
+    float z[MOE_MAX_LOGITS_PER_LANE];                  // lane l keeps the logits of experts l, l + 32, ...
+#pragma unroll
+    for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) z[r] = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+        const TW* w = wr + (size_t)e * D;
+        float acc = 0.0f;
+        for (int d = lane; d < D; d += 32) acc = fmaf(fb_to_float(x[d]), fb_to_float(w[d]), acc);
+        acc = fb_warp_sum(acc) + (br ? fb_to_float(br[e]) : 0.0f);
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r)
+            if (e == lane + 32 * r) z[r] = acc;
+    }
+    if (w_gate) {
+        float acc = 0.0f;
+        for (int d = lane; d < D; d += 32) acc = fmaf(fb_to_float(x[d]), fb_to_float(w_gate[d]), acc);
+        acc = fb_warp_sum(acc);
+        if (lane == 0) gate[row] = 1.0f / (1.0f + expf(-acc));
+    }
+    float first = 0.0f, total = 0.0f, mine = 0.0f;     // lane k keeps the k-th chosen logit (K <= 32)
+    for (int k = 0; k < K; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) {
+            const int e = lane + 32 * r;
+            if (e < E && (z[r] > best)) { best = z[r]; best_e = e; }     // ascending e: the lower index stays on a tie
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r)
+            if (best_e == lane + 32 * r) z[r] = -INFINITY;               // taken
+        if (k == 0) first = best;
+        const float p = expf(best - first);            // the first chosen logit is the largest
+        total += p;
+        if (lane == k) mine = p;
+        if (lane == 0) chosen[(size_t)row * K + k] = best_e;
+    }
+    if (lane < K) share[(size_t)row * K + lane] = mine / total;
+}
+
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ chosen, int pairs, int K, int E, int tile, int max_tiles,
+                int* __restrict__ place_token, int* __restrict__ pair_place, int* __restrict__ tile_expert) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    extern __shared__ int shi[];                       // [E] counts, then [E] cursors
+    int* count = shi;
+    int* cursor = shi + E;
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += blockDim.x) count[e] = 0;
+    for (int i = tid; i < max_tiles; i += blockDim.x) tile_expert[i] = -1;
+    for (int i = tid; i < max_tiles * tile; i += blockDim.x) place_token[i] = -1;
+    __syncthreads();
+    for (int p = tid; p < pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            cursor[e] = at;
+            const int tiles = (count[e] + tile - 1) / tile;
+            for (int t = 0; t < tiles; ++t) tile_expert[at / tile + t] = e;
+            at += tiles * tile;
+        }
+    }
+    __syncthreads();
+    for (int p = tid; p < pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        if (e < 0 || e >= E) { pair_place[p] = -1; continue; }
+        const int at = atomicAdd(&cursor[e], 1);
+        place_token[at] = p / K;
+        pair_place[p] = at;
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ expert_out, long expert_stride,
+                                   const int* __restrict__ pair_place, const float* __restrict__ share, int K,
+                                   const float* __restrict__ shared_out, int shared_partials, long shared_partial_stride,
+                                   const float* __restrict__ gate, float* __restrict__ out, int n, int D) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * D) return;
+    const int row = (int)(idx / D), c = (int)(idx - (size_t)row * D);
+    float acc = 0.0f;
+    for (int k = 0; k < K; ++k) {
+        const int at = pair_place[(size_t)row * K + k];
+        if (at >= 0) acc = fmaf(share[(size_t)row * K + k], expert_out[(size_t)at * expert_stride + c], acc);
+    }
+    if (shared_out) {
+        float s = 0.0f;
+        for (int p = 0; p < shared_partials; ++p) s += shared_out[(size_t)p * shared_partial_stride + idx];
+        acc = fmaf(gate ? gate[row] : 1.0f, s, acc);
+    }
+    out[idx] = acc;
+}
+
+FB_API int fb_moe_route(const void* h, long long h_stride, int h_dtype, const void* wr, const void* br,
+                        const void* w_gate, int w_dtype, int n, int D, int E, int K, int* chosen, float* share,
+                        float* gate, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && D > 0 && E > 0 && K > 0 && K <= E, "router: bad sizes n=%d width=%d experts=%d top=%d", n, D, E, K);
+    FB_REQUIRE(E <= 32 * MOE_MAX_LOGITS_PER_LANE, "router: %d experts are more than %d", E, 32 * MOE_MAX_LOGITS_PER_LANE);
+    FB_REQUIRE(K <= 32, "router: top = %d is more than 32", K);
+    FB_REQUIRE(!w_gate || gate, "router: a gate weight without a place for the gate");
+    if (n == 0) return 0;
+    FB_DISPATCH_DTYPE(h_dtype, T, FB_DISPATCH_DTYPE(w_dtype, TW,
+        (fb_launch((moe_route_kernel<T, TW>), dim3((n + 3) / 4), dim3(128), 0, stream, (const T*)h, (long)h_stride,
+                   (const TW*)wr, (const TW*)br, (const TW*)w_gate, n, D, E, K, chosen, share, gate))));
+    return fb_check_launch("moe_route");
+}
+
+// Row tiles the padded order can take at most: every full tile of pairs, and one ragged tile per expert that has any.
+FB_API int fb_moe_max_tiles(int pairs, int E, int tile) {
+    return pairs / tile + (E < pairs ? E : pairs);
+}
+
+FB_API int fb_moe_sort(const int* chosen, int pairs, int K, int E, int tile, int max_tiles, int* place_token,
+                       int* pair_place, int* tile_expert, cudaStream_t stream) {
+    FB_REQUIRE(pairs >= 0 && K > 0 && E > 0 && tile > 0, "moe_sort: bad sizes");
+    FB_REQUIRE(max_tiles >= fb_moe_max_tiles(pairs, E, tile), "moe_sort: %d row tiles are too few", max_tiles);
+    if (pairs == 0) return 0;
+    fb_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, chosen, pairs, K, E, tile,
+              max_tiles, place_token, pair_place, tile_expert);
+    return fb_check_launch("moe_sort");
+}
+
+FB_API int fb_moe_combine(const float* expert_out, long long expert_stride, const int* pair_place, const float* share,
+                          int K, const float* shared_out, int shared_partials, long long shared_partial_stride,
+                          const float* gate, float* out, int n, int D, cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && D > 0 && K > 0, "moe_combine: bad sizes");
+    if (n == 0) return 0;
+    const size_t total = (size_t)n * D;
+    fb_launch(moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, expert_out,
+              (long)expert_stride, pair_place, share, K, shared_out, shared_partials < 1 ? 1 : shared_partials,
+              (long)shared_partial_stride, gate, out, n, D);
+    return fb_check_launch("moe_combine");
+}

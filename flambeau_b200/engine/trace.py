@@ -62,7 +62,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--max-requests", type=int, default=8)
+    ap.add_argument("--max-requests", type=int, default=4, help="live requests at most (state slots)")
     args = ap.parse_args(argv)
     tokens = max(64, -(-args.max_tokens // 64) * 64)
 

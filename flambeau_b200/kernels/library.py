@@ -33,14 +33,31 @@ _SIGNATURES = {
     "fb_rope_table": (I, [P, P, P, P, I, I, STREAM]),
     "fb_rope_kv_write": (I, [P, L, I, L, P, L, P, L, P, L, I, I, P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P, STREAM]),
     "fb_gate_mul": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
+    "fb_activation": (I, [P, L, I, I, L, P, I, I, I, I, STREAM]),
+    "fb_add_row": (I, [P, P, I, I, I, STREAM]),
+    "fb_add_slabs": (I, [P, P, I, L, I, I, STREAM]),
+    "fb_branch_norm_mix": (I, [I, P, P, P, P, I, P, F, F, P, I, I, STREAM]),
     # gemm_simt.cu
     "fb_gemm_simt": (I, [P, I, L, P, I, L, P, I, L, I, I, I, STREAM]),
+    "fb_gemm_simt_grouped": (I, [P, I, L, P, P, I, L, L, P, I, P, I, L, I, I, I, I, STREAM]),
     # gemm_tc.cu
     "fb_gemm_tc_add": (I, [P, L, P, L, P, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
-    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, F, P, P, STREAM]),
+    "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, F, P, P, P, STREAM]),
+    # qk_norm_rope.cu
+    "fb_qk_norm_rope_kv_write": (I, [P, L, I, L, P, P, I, I, F, F, P, P, I, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I,
+                                     I, I, I, P, STREAM]),
+    # gated_delta.cu
+    "fb_gdr_prepare": (I, [P, L, I, L, P, I, P, P, I, P, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, F, STREAM]),
+    "fb_gdr_recurrent": (I, [P, P, P, P, L, P, P, P, I, P, I, I, I, I, STREAM]),
+    "fb_gdr_out_norm": (I, [P, P, L, I, L, I, P, I, F, P, I, I, I, I, STREAM]),
+    # moe.cu
+    "fb_moe_route": (I, [P, L, I, P, P, P, I, I, I, I, I, P, P, P, STREAM]),
+    "fb_moe_max_tiles": (I, [I, I, I]),
+    "fb_moe_sort": (I, [P, I, I, I, I, I, P, P, P, STREAM]),
+    "fb_moe_combine": (I, [P, L, P, P, I, P, I, L, P, P, I, I, STREAM]),
     # diff_attention.cu
     "fb_qkv_bias_cache_write": (I, [P, L, I, L, P, I, P, L, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, P,
                                     STREAM]),

@@ -268,6 +268,88 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, n_partials: int = 1, part
     gate_mul(gate_up, out, n_partials, partial_stride, "silu")
 
 
+PLAIN_ACTIVATIONS = {None: 0, "none": 0, "silu": 1, "gelu_tanh": 2, "relu_squared": 3}   # activations without a gate
+
+
+def plain_activation_code(name) -> int:
+    try:
+        return PLAIN_ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation '{name}' is not one of {sorted(str(k) for k in PLAIN_ACTIVATIONS)}") from None
+
+
+def activation(z: torch.Tensor, out: torch.Tensor, name: str, n_partials: int = 1, partial_stride: int = 0) -> None:
+    """out = act(z), z possibly the first of n_partials split-K shares `partial_stride` elements apart."""
+    _cuda(z, out)
+    n, I = z.shape
+    if tuple(out.shape) != (n, I) or not out.is_contiguous():
+        raise KernelError("activation: bad output")
+    check(lib().fb_activation(z.data_ptr(), _rows(z), dtype_code(z), int(n_partials), int(partial_stride),
+                              out.data_ptr(), dtype_code(out), n, I, plain_activation_code(name), _stream()),
+          "activation")
+
+
+def add_row(x: torch.Tensor, v: torch.Tensor) -> None:
+    """x[r] += v for every row of the contiguous float32 x."""
+    _cuda(x, v)
+    n, H = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or v.numel() != H or not v.is_contiguous():
+        raise KernelError("add_row: a contiguous float32 [n, H] and a vector of H wanted")
+    check(lib().fb_add_row(x.data_ptr(), v.data_ptr(), dtype_code(v), n, H, _stream()), "add_row")
+
+
+def add_slabs(x: torch.Tensor, delta: torch.Tensor, n: int, n_partials: int = 1, partial_stride: int = 0) -> None:
+    """x[:n] += delta[:n] (and the further shares of delta, `partial_stride` elements apart); contiguous float32."""
+    _cuda(x, delta)
+    if x.dtype != torch.float32 or delta.dtype != torch.float32 or not x.is_contiguous() or not delta.is_contiguous() \
+            or x.shape[1] != delta.shape[-1]:
+        raise KernelError("add_slabs: contiguous float32 rows of one width wanted")
+    check(lib().fb_add_slabs(x.data_ptr(), delta.data_ptr(), int(n_partials), int(partial_stride), int(n), x.shape[1],
+                             _stream()), "add_slabs")
+
+
+def branch_norm_mix(branches, eps: float, out: torch.Tensor, n: int, weight_offset: float = 0.0) -> None:
+    """out[r] = sum_b coef_b * rmsnorm(y_b[r]) * (w_b + weight_offset) for the first n rows.  `branches`: tuples
+    (y float32 [n, H] or the first of its shares, n_partials, partial_stride, weight [H], coef); the weights share
+    one dtype."""
+    H = out.shape[1]
+    B = len(branches)
+    ys = (ctypes.c_void_p * B)(*[y.data_ptr() for y, *_ in branches])
+    parts = (ctypes.c_int * B)(*[int(p) for _, p, *_ in branches])
+    strides = (ctypes.c_longlong * B)(*[int(s) for _, _, s, *_ in branches])
+    ws = (ctypes.c_void_p * B)(*[w.data_ptr() for *_, w, _ in branches])
+    coefs = (ctypes.c_float * B)(*[float(c) for *_, c in branches])
+    for y, _, _, w, _ in branches:
+        _cuda(y, w)
+        if y.dtype != torch.float32 or y.shape[-1] != H or not y.is_contiguous() or w.numel() != H \
+                or w.dtype != branches[0][3].dtype:
+            raise KernelError("branch_norm_mix: float32 branches of the output's width, weights of one dtype")
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.shape[0] < n:
+        raise KernelError("branch_norm_mix: a contiguous float32 output wanted")
+    check(lib().fb_branch_norm_mix(B, ys, parts, strides, ws, dtype_code(branches[0][3]), coefs, float(eps),
+                                   float(weight_offset), out.data_ptr(), int(n), H, _stream()), "branch_norm_mix")
+
+
+def gemm_simt_grouped(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torch.Tensor, tile: int,
+                      out: torch.Tensor, activation_name=None) -> None:
+    """out[m] = act(a[row_index[m]] @ w[tile_group[m // tile]]^T): w is [groups, N, K]; the rows of `out` come in
+    tiles of `tile` (16 or 64) that belong to one group each (negative: skipped); row_index negative = a row of
+    zeros, None = row m itself."""
+    _cuda(a, row_index, w, tile_group, out)
+    _i32(row_index, "row_index")
+    _i32(tile_group, "tile_group")
+    if w.dim() != 3 or not w.is_contiguous():
+        raise KernelError("grouped gemm: weights are contiguous [groups, N, K]")
+    _, N, K = w.shape
+    M = out.shape[0]
+    if a.shape[1] != K or out.shape[1] != N or tile_group.numel() * tile < M:
+        raise KernelError("grouped gemm: shapes do not agree")
+    check(lib().fb_gemm_simt_grouped(a.data_ptr(), dtype_code(a), _rows(a), _ptr(row_index), w.data_ptr(),
+                                     dtype_code(w), K, N * K, tile_group.data_ptr(), int(tile), out.data_ptr(),
+                                     dtype_code(out), _rows(out), M, N, K, plain_activation_code(activation_name),
+                                     _stream()), "gemm_simt_grouped", (M, N, K))
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = a[M,K] @ w[N,K]^T, float32 accumulation on the CUDA cores."""
     _cuda(a, w, out)
@@ -290,15 +372,22 @@ def _slopes(score_slopes, nh: int) -> int:
 
 
 def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq, nh: int, nkv: int, hd: int,
-                         window: int, scale: float, status, table_base=None, score_slopes=None) -> None:
+                         window: int, scale: float, status, table_base=None, score_slopes=None, sinks=None,
+                         vd: int = 0) -> None:
     """score_slopes (float32 per query head, optional): slope * (key position - query position) is added to every
-    scaled score, a linear penalty on distance."""
-    _cuda(q, out, k_pool, v_pool, block_table, positions, row_seq, status, table_base)
+    scaled score, a linear penalty on distance.  sinks (float32 per query head, optional): one more softmax slot per
+    head whose score is that number, unscaled, and which has no value.  vd: the size of a value row where it is not
+    the key row's (the output then has nh * vd columns)."""
+    _cuda(q, out, k_pool, v_pool, block_table, positions, row_seq, status, table_base, sinks)
     _i32(table_base, "table_base")
     n = q.shape[0]
+    vd = int(vd) or hd
     n_pages, pool_kv, page_size, pool_hd = k_pool.shape
-    if pool_kv != nkv or pool_hd != hd or q.shape[1] != nh * hd or out.shape[1] != nh * hd or out.shape[0] != n:
+    if pool_kv != nkv or pool_hd != hd or q.shape[1] != nh * hd or out.shape[1] != nh * vd or out.shape[0] != n \
+            or tuple(v_pool.shape) != (n_pages, nkv, page_size, vd):
         raise KernelError("attention: shapes do not match the head counts")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nh or not sinks.is_contiguous()):
+        raise KernelError("attention: sinks are one float32 per query head")
     if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype):
         raise KernelError("attention: q, out and the cache must share one dtype")
     if not k_pool.is_contiguous() or not v_pool.is_contiguous():
@@ -306,8 +395,8 @@ def paged_attention_simt(q, out, k_pool, v_pool, block_table, positions, row_seq
     check(lib().fb_paged_attention_simt(
         q.data_ptr(), _rows(q), out.data_ptr(), _rows(out), dtype_code(q), k_pool.data_ptr(), v_pool.data_ptr(),
         page_size, n_pages, block_table.data_ptr(), block_table.stride(0), _ptr(table_base), positions.data_ptr(),
-        row_seq.data_ptr(), n, nh, nkv, hd, int(window), float(scale), _slopes(score_slopes, nh), status.data_ptr(),
-        _stream()), "paged_attention_simt")
+        row_seq.data_ptr(), n, nh, nkv, hd, vd, int(window), float(scale), _slopes(score_slopes, nh), _ptr(sinks),
+        status.data_ptr(), _stream()), "paged_attention_simt")
 
 
 def apply_penalties(logits, rows, tokens, counts, repetition, presence, frequency) -> None:
@@ -440,6 +529,13 @@ def linear_slabs(a: torch.Tensor, w: torch.Tensor, slabs: torch.Tensor, ctx) -> 
     return 1
 
 
+def grouped_linear(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torch.Tensor, tile: int,
+                   out: torch.Tensor, activation_name=None, ctx=None) -> None:
+    """out[m] = act(a[row_index[m]] @ w[tile_group[m // tile]]^T) with w [groups, N, K]: the product of routed
+    experts over rows that were sorted by expert and padded to whole tiles (see gemm_simt_grouped)."""
+    gemm_simt_grouped(a, row_index, w, tile_group, tile, out, activation_name)
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ctx=None) -> None:
     """out = a @ w^T with the kernel that fits the dtypes and the shape: the tcgen05 kernel for bfloat16
     operands it can fetch by TMA, the float32-FMA kernel for everything else (all of the 32-bit mode)."""
@@ -540,12 +636,13 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
 
 
 def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float,
-                    next_weight=None, score_slopes=None) -> None:
+                    next_weight=None, score_slopes=None, sinks=None, vd: int = 0) -> None:
     """Attention of every row of the step over its request's cached keys: the tensor-core kernel for bfloat16
     and head sizes it takes, the float32 CUDA-core kernel otherwise (all of the 32-bit mode).  next_weight: the
     matrix of the product that follows, whose start the bfloat16 kernel may fetch into L2 (a hint)."""
     b = ctx.batch
-    if mma_attention_supported(q, nh, nkv, hd):
+    vd = int(vd) or hd
+    if mma_attention_supported(q, nh, nkv, hd) and sinks is None and vd == hd:
         G = nh // nkv
         short = [ql * G <= 16 for ql in b.seq_q_len]
         paged_attention_mma(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.seq_q_start_d, b.seq_q_len_d,
@@ -556,7 +653,7 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
     else:
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
                              nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
-                             score_slopes=score_slopes)
+                             score_slopes=score_slopes, sinks=sinks, vd=vd)
 
 
 def diff_attention_mma_supported(q: torch.Tensor, nh: int, nkv: int, kd: int, vd: int) -> bool:
@@ -630,3 +727,137 @@ def set_diff_attention_mma(on: bool) -> None:
     """Differential attention in bfloat16 on the tensor-core arrangements where they take the geometry (the default),
     or always on the float32-math kernel."""
     _DIFF_MMA[0] = bool(on)
+
+
+# ---------------------------------------------------------------------------
+# query/key norm + rotation + cache write behind a fused projection
+# ---------------------------------------------------------------------------
+QK_NORM_REACH = {None: 0, "none": 0, "head": 1, "projection": 2}
+
+
+def qk_norm_rope_kv_write(proj: torch.Tensor, q_weight, k_weight, reach, eps: float, weight_offset: float, cos, sin,
+                          half: int, q_out: torch.Tensor, cache, positions, row_seq, nh: int, nkv: int, hd: int,
+                          vd: int, status, n_partials: int = 1, partial_stride: int = 0) -> None:
+    """proj: float32 rows [q: nh*hd | k: nkv*hd | v: nkv*vd] (possibly split-K shares).  q and k pass an RMS norm
+    whose reach is a head ('head': weights [hd]) or the whole projection ('projection': weights [nh*hd] and
+    [nkv*hd]) or none, then the rotation of the first 2*half dimensions of every head (cos/sin float32 [n, half]);
+    q goes to q_out in its dtype, k and v into the cache's pages when the view is writable."""
+    _cuda(proj, q_weight, k_weight, cos, sin, q_out, positions, row_seq, status)
+    n = proj.shape[0]
+    code = QK_NORM_REACH[reach]
+    if proj.dtype != torch.float32 or tuple(q_out.shape) != (n, nh * hd):
+        raise KernelError("qk_norm_rope_kv_write: float32 projection rows and q [n, heads * size] wanted")
+    if code:
+        want = (hd, hd) if code == 1 else (nh * hd, nkv * hd)
+        if q_weight is None or k_weight is None or (q_weight.numel(), k_weight.numel()) != want \
+                or q_weight.dtype != k_weight.dtype:
+            raise KernelError("qk_norm_rope_kv_write: the norm weights do not fit the norm's reach")
+    k_pool, v_pool = cache.k_pool, cache.v_pool
+    n_pages = k_pool.shape[0]
+    if tuple(k_pool.shape) != (n_pages, nkv, cache.page_size, hd) or tuple(v_pool.shape) != (n_pages, nkv, cache.page_size, vd) \
+            or not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.dtype != q_out.dtype:
+        raise KernelError("qk_norm_rope_kv_write: the cache pools do not fit the head sizes")
+    check(lib().fb_qk_norm_rope_kv_write(
+        proj.data_ptr(), _rows(proj), int(n_partials), int(partial_stride), _ptr(q_weight), _ptr(k_weight),
+        dtype_code(q_weight) if q_weight is not None else 0, code, float(eps), float(weight_offset), _ptr(cos),
+        _ptr(sin), int(half), q_out.data_ptr(), _rows(q_out), dtype_code(q_out), positions.data_ptr(),
+        row_seq.data_ptr(), cache.block_table.data_ptr(), cache.block_table.stride(0), _ptr(cache.table_base),
+        k_pool.data_ptr(), v_pool.data_ptr(), cache.page_size, n_pages, n, nh, nkv, hd, vd,
+        1 if cache.writable else 0, status.data_ptr(), _stream()), "qk_norm_rope_kv_write")
+
+
+# ---------------------------------------------------------------------------
+# gated delta rule
+# ---------------------------------------------------------------------------
+def gdr_prepare(proj, conv_w, taps: int, a_log, dt_bias, state, tail_off: int, batch, qkv, beta, decay, G: int,
+                H: int, dk: int, dv: int, q_scale: float, unit_eps: float, n_partials: int = 1,
+                partial_stride: int = 0) -> None:
+    """The step's tokens made ready for the recurrence (csrc/gated_delta.cu: gdr_prepare, gdr_conv_tail).  proj:
+    float32 rows [q | k | v | b | a | gate] (possibly shares); state: float32 [slots, floats per slot] with the
+    convolution's tail at `tail_off`; qkv, beta, decay: float32 outputs [n, C], [n, H], [n, H]."""
+    _cuda(proj, conv_w, a_log, dt_bias, state, qkv, beta, decay)
+    n = proj.shape[0]
+    C = 2 * G * dk + H * dv
+    if proj.dtype != torch.float32 or state.dtype != torch.float32 or not state.is_contiguous() or state.dim() != 2 \
+            or tuple(qkv.shape) != (n, C) or tuple(beta.shape) != (n, H) or tuple(decay.shape) != (n, H) \
+            or tuple(conv_w.shape) != (C, taps) or not conv_w.is_contiguous() \
+            or not (conv_w.dtype == a_log.dtype == dt_bias.dtype) \
+            or any(t.dtype != torch.float32 or not t.is_contiguous() for t in (qkv, beta, decay)):
+        raise KernelError("gated delta: bad shapes or dtypes")
+    if state.shape[1] < tail_off + (taps - 1) * C:
+        raise KernelError("gated delta: the state slot is too small for the convolution's tail")
+    check(lib().fb_gdr_prepare(proj.data_ptr(), _rows(proj), int(n_partials), int(partial_stride), conv_w.data_ptr(),
+                               int(taps), a_log.data_ptr(), dt_bias.data_ptr(), dtype_code(conv_w), state.data_ptr(),
+                               state.stride(0), int(tail_off), batch.row_seq.data_ptr(), batch.seq_q_start_d.data_ptr(),
+                               batch.seq_q_len_d.data_ptr(), batch.seq_slot_d.data_ptr(), batch.n_seqs,
+                               qkv.data_ptr(), beta.data_ptr(), decay.data_ptr(), n, G, H, dk, dv, float(q_scale),
+                               float(unit_eps), _stream()), "gdr_prepare")
+
+
+def gdr_recurrent(qkv, beta, decay, state, batch, o, G: int, H: int, dk: int, dv: int) -> None:
+    """S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over the step's tokens of every request, the state
+    [H][dk][dv] at the start of the request's slot."""
+    _cuda(qkv, beta, decay, state, o)
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.shape[1] != H * dv or state.shape[1] < H * dk * dv:
+        raise KernelError("gated delta: bad output or state")
+    check(lib().fb_gdr_recurrent(qkv.data_ptr(), beta.data_ptr(), decay.data_ptr(), state.data_ptr(), state.stride(0),
+                                 batch.seq_q_start_d.data_ptr(), batch.seq_q_len_d.data_ptr(),
+                                 batch.seq_slot_d.data_ptr(), batch.n_seqs, o.data_ptr(), G, H, dk, dv, _stream()),
+          "gdr_recurrent")
+
+
+def gdr_out_norm(o, proj, gate_off: int, weight, eps: float, out, H: int, dv: int, n_partials: int = 1,
+                 partial_stride: int = 0) -> None:
+    """out = o / rms(o) * weight * silu(gate) per head, the gate taken from the projection rows at `gate_off`."""
+    _cuda(o, proj, weight, out)
+    n = o.shape[0]
+    if tuple(out.shape) != (n, H * dv) or not out.is_contiguous() or weight.numel() != dv:
+        raise KernelError("gated delta: bad output")
+    check(lib().fb_gdr_out_norm(o.data_ptr(), proj.data_ptr(), _rows(proj), int(n_partials), int(partial_stride),
+                                int(gate_off), weight.data_ptr(), dtype_code(weight), float(eps), out.data_ptr(),
+                                dtype_code(out), n, H, dv, _stream()), "gdr_out_norm")
+
+
+# ---------------------------------------------------------------------------
+# routed experts
+# ---------------------------------------------------------------------------
+def moe_route(h, wr, br, w_gate, top: int, chosen, share, gate) -> None:
+    """Per token: the `top` experts with the largest router logits (float32), their softmax weights, and (with
+    w_gate) sigmoid(w_gate . h)."""
+    _cuda(h, wr, br, w_gate, chosen, share, gate)
+    n, D = h.shape
+    E = wr.shape[0]
+    if tuple(chosen.shape) != (n, top) or chosen.dtype != torch.int32 or tuple(share.shape) != (n, top) \
+            or share.dtype != torch.float32 or not wr.is_contiguous() or wr.shape[1] != D:
+        raise KernelError("router: bad shapes")
+    check(lib().fb_moe_route(h.data_ptr(), _rows(h), dtype_code(h), wr.data_ptr(), _ptr(br), _ptr(w_gate),
+                             dtype_code(wr), n, D, E, int(top), chosen.data_ptr(), share.data_ptr(), _ptr(gate),
+                             _stream()), "moe_route")
+
+
+def moe_max_tiles(pairs: int, experts: int, tile: int) -> int:
+    return pairs // tile + min(experts, pairs)
+
+
+def moe_sort(chosen, experts: int, tile: int, place_token, pair_place, tile_expert) -> None:
+    """The (token, choice) pairs in expert order, every expert's stretch padded to whole row tiles."""
+    _cuda(chosen, place_token, pair_place, tile_expert)
+    n, K = chosen.shape
+    check(lib().fb_moe_sort(chosen.data_ptr(), n * K, K, int(experts), int(tile), tile_expert.numel(),
+                            place_token.data_ptr(), pair_place.data_ptr(), tile_expert.data_ptr(), _stream()),
+          "moe_sort")
+
+
+def moe_combine(expert_out, pair_place, share, shared_out, shared_partials: int, shared_partial_stride: int, gate,
+                out, n: int) -> None:
+    """out[t] = sum_k share[t, k] * expert_out[pair_place[t, k]] + gate[t] * sum of shared_out's shares."""
+    _cuda(expert_out, pair_place, share, shared_out, gate, out)
+    D = out.shape[1]
+    K = share.shape[1]
+    if expert_out.dtype != torch.float32 or out.dtype != torch.float32 or not out.is_contiguous() \
+            or expert_out.shape[1] != D or (shared_out is not None and (shared_out.dtype != torch.float32
+                                                                        or not shared_out.is_contiguous())):
+        raise KernelError("moe_combine: float32 rows of the output's width wanted")
+    check(lib().fb_moe_combine(expert_out.data_ptr(), _rows(expert_out), pair_place.data_ptr(), share.data_ptr(), K,
+                               _ptr(shared_out), int(shared_partials), int(shared_partial_stride), _ptr(gate),
+                               out.data_ptr(), int(n), D, _stream()), "moe_combine")

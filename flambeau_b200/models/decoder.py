@@ -82,7 +82,7 @@ class DecoderModel:
             stream.x.copy_(x0)
         for ci, call in enumerate(self.order):
             if call.reenter:
-                self.reentry.forward(ctx, stream, x0)
+                self.reentry.forward(ctx, stream, x0, call.pass_index)
             self.layers[call.layer].forward(ctx, stream, ci)
         if b.n_out == 0:
             return None

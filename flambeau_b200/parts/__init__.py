@@ -1,5 +1,6 @@
 """Parts: import the built-in ones so that they are registered."""
-from . import attention, block, diff_attention, embedding, feedforward, norms, positions, reentry  # noqa: F401
+from . import (attention, block, diff_attention, embedding, feedforward, gated_delta, moe, norms, parallel,  # noqa: F401
+               positions, reentry)
 from .base import (FeedForward, KVRequirement, Mixer, Norm, Part, PositionEncoding, StateRequirement,  # noqa: F401
                    TensorSpec)
 from .spec import (LayerCall, ModelSpec, PartSpec, build_part, part_class, register_part,  # noqa: F401

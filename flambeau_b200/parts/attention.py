@@ -29,14 +29,34 @@ class PagedAttention(Mixer):
     position - query position) is added to every scaled score, a linear
     penalty on distance that a position scheme without rotation can be built
     from (the architecture built here has none; portions of prompts then run
-    on the mma.sync kernel, which has the hook)."""
+    on the mma.sync kernel, which has the hook).
+    `qk_norm_reach`: 'head' (the default: every head of q and of k is normalised alone, weights of head_dim) or
+    'projection' (one norm over all of q and one over all of k before they are split into heads, weights of
+    num_heads * head_dim and num_kv_heads * head_dim).
+    `value_dim`: the size of a value row where it is not head_dim; the output projection then takes
+    num_heads * value_dim columns.
+    `sink` (bool): the softmax of every head has one more slot, a learned score per head (`<prefix><names.sink>`,
+    [num_heads]) that is not scaled, has no key and no value, and counts once in the denominator.
+    `names`: what the tensors are called behind the prefix (keys q, k, v, o, q_norm, k_norm, sink), for checkpoints
+    with other names than the defaults."""
     graph_safe = True
+
+    DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                     "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks"}
 
     def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  window: int = 0, position: PartSpec | None = None, scale: float | None = None,
-                 init_std: float = 0.02, qk_norm: PartSpec | None = None, distance_slopes=None):
+                 init_std: float = 0.02, qk_norm: PartSpec | None = None, distance_slopes=None,
+                 qk_norm_reach: str = "head", value_dim: int | None = None, sink: bool = False, names=None):
         super().__init__(runtime, prefix)
         self.width, self.nh, self.nkv, self.hd = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.vd = int(value_dim) if value_dim else self.hd
+        self.sink = bool(sink)
+        self.names = dict(self.DEFAULT_NAMES)
+        self.names.update(names or {})
+        if qk_norm_reach not in ("head", "projection"):
+            raise ValueError(f"qk_norm_reach = {qk_norm_reach!r}: 'head' or 'projection'")
+        self.qk_norm_reach = qk_norm_reach
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} query heads are not a multiple of {self.nkv} key/value heads")
         self.window = int(window or 0)
@@ -44,8 +64,18 @@ class PagedAttention(Mixer):
         self.position = build_part(position, runtime) if position is not None else None
         self.q_norm = self.k_norm = None
         if qk_norm is not None:
-            self.q_norm = build_part(PartSpec(qk_norm.category, qk_norm.kind, qk_norm.params, prefix + "q_norm."), runtime)
-            self.k_norm = build_part(PartSpec(qk_norm.category, qk_norm.kind, qk_norm.params, prefix + "k_norm."), runtime)
+            def norm_part(name, width_of_projection):
+                # "<base>.<leaf>" behind the mixer's prefix: the norm part gets the prefix up to the last dot and
+                # the leaf as the name of its weight
+                params = dict(qk_norm.params)
+                base, _, leaf = self.names[name].rpartition(".")
+                params.setdefault("weight_name", leaf)
+                if qk_norm_reach == "projection":
+                    params["width"] = width_of_projection
+                return build_part(PartSpec(qk_norm.category, qk_norm.kind, params,
+                                           prefix + (base + "." if base else "")), runtime)
+            self.q_norm = norm_part("q_norm", self.nh * self.hd)
+            self.k_norm = norm_part("k_norm", self.nkv * self.hd)
         self.init_std = init_std
         self.distance_slopes = None
         if distance_slopes is not None:
@@ -54,32 +84,51 @@ class PagedAttention(Mixer):
                 raise ValueError(f"{len(slopes)} distance slopes for {self.nh} query heads")
             self.distance_slopes = torch.tensor(slopes, dtype=torch.float32,
                                                 device=runtime.device if runtime is not None else "cpu")
-        self.qw, self.kvw = self.nh * self.hd, self.nkv * self.hd
-        self.qkv = self.o = None
+        self.qw, self.kvw, self.vw = self.nh * self.hd, self.nkv * self.hd, self.nkv * self.vd
+        self.qkv = self.o = self.sinks = None
 
     def children(self):
         return [p for p in (self.position, self.q_norm, self.k_norm) if p is not None]
 
     def cache_requirement(self):
-        return KVRequirement(self.nkv, self.hd, self.window)
+        return KVRequirement(self.nkv, self.hd, self.window, v_head_dim=self.vd if self.vd != self.hd else 0)
 
     def own_tensor_specs(self):
         p, init = self.prefix, ("normal", self.init_std)
-        return {
-            p + "q_proj.weight": TensorSpec((self.qw, self.width), init=init),
-            p + "k_proj.weight": TensorSpec((self.kvw, self.width), init=init),
-            p + "v_proj.weight": TensorSpec((self.kvw, self.width), init=init),
-            p + "o_proj.weight": TensorSpec((self.width, self.qw), init=init),
+        nm = self.names
+        specs = {
+            p + nm["q"]: TensorSpec((self.qw, self.width), init=init),
+            p + nm["k"]: TensorSpec((self.kvw, self.width), init=init),
+            p + nm["v"]: TensorSpec((self.vw, self.width), init=init),
+            p + nm["o"]: TensorSpec((self.width, self.nh * self.vd), init=init),
         }
+        if self.sink:
+            specs[p + nm["sink"]] = TensorSpec((self.nh,), init=("normal", 1.0))
+        return specs
 
     def own_bind(self, tensors):
-        p = self.prefix
-        self.qkv = Linear(concat_rows([tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"],
-                                       tensors[p + "v_proj.weight"]]))
-        self.o = Linear(tensors[p + "o_proj.weight"])
+        p, nm = self.prefix, self.names
+        stack = [tensors[p + nm["q"]], tensors[p + nm["k"]], tensors[p + nm["v"]]]
+        rows = sum(t.shape[0] for t in stack)
+        if rows % 8 and (self.q_norm is not None or self.vd != self.hd) and self._fused_norm_kernel():
+            # rows of zeros up to a multiple of 8, so that the product's float32 rows stay 16-byte aligned
+            stack.append(torch.zeros((8 - rows % 8, self.width), dtype=stack[0].dtype, device=stack[0].device))
+        self.qkv = Linear(concat_rows(stack))
+        self.o = Linear(tensors[p + nm["o"]])
+        if self.sink:
+            self.sinks = tensors[p + nm["sink"]].float().contiguous()      # scores are float32 in both modes
 
     def own_weights(self):
         return [self.qkv.weight, self.o.weight]
+
+    def _fused_norm_kernel(self) -> bool:
+        """Whether the kernel that normalises, rotates and writes the cache in one pass serves this mixer: the norms
+        (if any) are the framework's RMS norm and the position encoding hands out its tables."""
+        from .norms import RMSNorm
+        pos = self.position
+        if pos is not None and not getattr(pos, "fused_with_cache_write", False):
+            return False
+        return all(n is None or type(n) is RMSNorm for n in (self.q_norm, self.k_norm))
 
     def forward(self, ctx, h, out, call):
         n = ctx.n_tokens
@@ -91,6 +140,29 @@ class PagedAttention(Mixer):
             fused = pos is None or getattr(pos, "fused_with_cache_write", False)
             # the fused rotary kernel adds split-K shares of the projection itself; a position encoding with a
             # rotate() of its own gets whole rows
+            if (self.q_norm is not None or self.vd != self.hd) and self._fused_norm_kernel():
+                # one product for q, k and v; one kernel adds its shares, normalises q and k (every head alone or
+                # the whole projection at once), rotates them, rounds q and fills the cache's pages
+                cols = self.qkv.out_features
+                slabs = ctx.ws.alloc((ctx.max_slabs, n, cols), torch.float32)
+                parts = self.qkv.slabs(ctx, h, slabs)
+                q = ctx.ws.alloc((n, self.qw), rt.dtype)
+                cos, sin = pos.prepare(ctx) if pos is not None else (None, None)
+                qn = self.q_norm
+                ops.qk_norm_rope_kv_write(
+                    slabs[0], qn.weight if qn is not None else None,
+                    self.k_norm.weight if qn is not None else None, self.qk_norm_reach if qn is not None else None,
+                    qn.eps if qn is not None else 0.0, qn.weight_offset if qn is not None else 0.0, cos, sin,
+                    pos.half if pos is not None else 0, q, cache, ctx.batch.positions, ctx.batch.row_seq, self.nh,
+                    self.nkv, self.hd, self.vd, rt.status, n_partials=parts, partial_stride=slabs.stride(0))
+                a = ctx.ws.alloc((n, self.nh * self.vd), rt.dtype)
+                ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
+                                    score_slopes=self.distance_slopes, sinks=self.sinks, vd=self.vd)
+                ctx.to_stream(self.o, a)
+                return
+            if self.vd != self.hd or self.qk_norm_reach != "head":
+                raise ValueError("attention: value rows of their own width, or a norm over the whole projection, "
+                                 "need the framework's RMS norm and a position encoding that hands out its tables")
             if self.q_norm is None:
                 qkv_slabs = ctx.ws.alloc((ctx.max_slabs if fused else 1, n, self.qw + 2 * self.kvw), torch.float32)
                 parts = self.qkv.slabs(ctx, h, qkv_slabs)
@@ -130,7 +202,7 @@ class PagedAttention(Mixer):
             # few rows: the attention kernel fetches the start of the output projection's weights into L2 at its end
             hint = self.o.weight if ctx.l2_hints and n <= 64 else None
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
-                                next_weight=hint, score_slopes=self.distance_slopes)
+                                next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks)
             ctx.to_stream(self.o, a)
 
 

@@ -1,6 +1,7 @@
 """How a layer arranges its norms, mixer and feed-forward around the stream."""
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import Part
 from .spec import PartSpec, build_part, register_part
 
@@ -22,9 +23,12 @@ class ResidualStream:
         """Add what is pending to x now (through the pending norm's kernel, which then normalises nothing else), for
         a part that wants the whole stream rather than a normalised copy of it."""
         if self.pending is None or self.pending_slabs == 0:
+            self.pending, self.pending_slabs, self.pending_norm = None, 0, None
             return
         if self.pending_norm is None:
-            raise ValueError("a pending output without a norm of its own is added by the next norm, not settled")
+            ops.add_slabs(self.x, self.pending, ctx.n_tokens, self.pending_slabs, ctx.delta_slabs.stride(0))
+            self.pending, self.pending_slabs = None, 0
+            return
         self.pending_norm.add_norm(ctx, self.x, self.pending, None, n_partials=self.pending_slabs,
                                    delta_norm=self.pending_norm)
         self.pending, self.pending_slabs, self.pending_norm = None, 0, None
@@ -32,20 +36,25 @@ class ResidualStream:
 
 class PreNormBlock(Part):
     """x = x + mixer(norm1(x)); x = x + feed_forward(norm2(x))
-    (crates/models/qwen35-v2/src/model.rs:25-42)."""
+    (crates/models/qwen35-v2/src/model.rs:25-42).  `feed_forward` (with its norm) may be None: the layer then ends
+    behind the mixer."""
     graph_safe = True
     category = "block"
 
-    def __init__(self, runtime=None, prefix="", *, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
-                 feed_forward_norm: PartSpec):
+    def __init__(self, runtime=None, prefix="", *, mixer: PartSpec, mixer_norm: PartSpec,
+                 feed_forward: PartSpec | None = None, feed_forward_norm: PartSpec | None = None):
         super().__init__(runtime, prefix)
         self.mixer = build_part(mixer, runtime)
-        self.feed_forward = build_part(feed_forward, runtime)
         self.mixer_norm = build_part(mixer_norm, runtime)
-        self.feed_forward_norm = build_part(feed_forward_norm, runtime)
+        self.feed_forward = self.feed_forward_norm = None
+        if feed_forward is not None:
+            if feed_forward_norm is None:
+                raise ValueError("a feed-forward behind a norm needs that norm")
+            self.feed_forward = build_part(feed_forward, runtime)
+            self.feed_forward_norm = build_part(feed_forward_norm, runtime)
 
     def children(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
 
     def forward(self, ctx, stream: ResidualStream, call) -> None:
         h, delta = ctx.normed, ctx.delta
@@ -56,10 +65,11 @@ class PreNormBlock(Part):
         ctx.pending_slabs = 1                 # a part that leaves split-K shares in ctx.delta_slabs says how many
         self.mixer.forward(ctx, h, delta, call)
         stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
-        self.feed_forward_norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs)
-        ctx.pending_slabs = 1
-        self.feed_forward.forward(ctx, h, delta)
-        stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
+        if self.feed_forward is not None:
+            self.feed_forward_norm.add_norm(ctx, stream.x, stream.pending, h, n_partials=stream.pending_slabs)
+            ctx.pending_slabs = 1
+            self.feed_forward.forward(ctx, h, delta)
+            stream.pending, stream.pending_slabs = delta, ctx.pending_slabs
         ctx.stream_x = None                   # another kind of block decides for itself whether parts may add to its stream
 
 

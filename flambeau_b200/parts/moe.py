@@ -1,0 +1,116 @@
+"""Routed experts: a feed-forward of many small feed-forwards of which every token uses a few."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, TensorSpec
+from .linear import Linear
+from .spec import register_part
+
+
+class RoutedExperts(FeedForward):
+    """d = sum over the token's `top` experts of share_e * Wdown_e act(Wup_e h)  (+ gate * shared(h))
+
+    Router logits z = Wr h + br are float32; the `top` experts with the largest logits are chosen (the lower index
+    wins a tie) and their shares are the softmax over the chosen logits only.  Experts have no biases and no gate
+    map; `activation` is one of kernels.ops.PLAIN_ACTIVATIONS.  With `shared_inner`, one more expert of that inner
+    size runs for every token and is added times sigmoid(w_sg . h), one number per token.
+
+    Tensors behind the prefix: e<i>.up [inner, width], e<i>.down [width, inner], router [experts, width], router.b
+    [experts], and with a shared expert shared.up, shared.down, shared.sg [1, width].
+
+    How a step runs: the router (one warp a token), a counting sort of the (token, choice) pairs into expert order
+    with every expert's stretch padded to whole row tiles, two grouped products over that order (the first gathers
+    the tokens' rows and applies the activation), and one kernel that brings the weighted outputs back to the
+    tokens and adds the shared expert.  All sizes on the host are upper bounds, so nothing is read back and the
+    step can be replayed from a CUDA graph."""
+    graph_safe = True
+
+    def __init__(self, runtime=None, prefix="", *, width: int, inner: int, experts: int, top: int,
+                 activation: str = "relu_squared", shared_inner: int | None = None, router_bias: bool = True,
+                 init_std: float = 0.02, router_std: float = 0.5):
+        super().__init__(runtime, prefix)
+        self.width, self.inner, self.E, self.K = int(width), int(inner), int(experts), int(top)
+        if not 1 <= self.K <= self.E:
+            raise ValueError(f"top = {self.K} of {self.E} experts")
+        if activation not in ops.PLAIN_ACTIVATIONS:
+            raise ValueError(f"routed experts: activation '{activation}' is not implemented")
+        self.activation = activation
+        self.shared_inner = int(shared_inner) if shared_inner else 0
+        self.router_bias, self.init_std, self.router_std = bool(router_bias), init_std, router_std
+        self.up = self.down = self.router = self.router_b = None
+        self.shared_up = self.shared_down = self.shared_gate = None
+
+    def own_tensor_specs(self):
+        p, init = self.prefix, ("normal", self.init_std)
+        specs = {}
+        for e in range(self.E):
+            specs[f"{p}e{e}.up"] = TensorSpec((self.inner, self.width), init=init)
+            specs[f"{p}e{e}.down"] = TensorSpec((self.width, self.inner), init=init)
+        specs[p + "router"] = TensorSpec((self.E, self.width), init=("normal", self.router_std))
+        if self.router_bias:
+            specs[p + "router.b"] = TensorSpec((self.E,), init=("normal", 0.1))
+        if self.shared_inner:
+            specs[p + "shared.up"] = TensorSpec((self.shared_inner, self.width), init=init)
+            specs[p + "shared.down"] = TensorSpec((self.width, self.shared_inner), init=init)
+            specs[p + "shared.sg"] = TensorSpec((1, self.width), init=init)
+        return specs
+
+    def own_bind(self, tensors):
+        p = self.prefix
+        self.up = torch.stack([tensors[f"{p}e{e}.up"] for e in range(self.E)]).contiguous()        # [E, inner, width]
+        self.down = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.E)]).contiguous()    # [E, width, inner]
+        self.router = tensors[p + "router"].contiguous()
+        self.router_b = tensors[p + "router.b"].to(self.router.dtype).contiguous() if self.router_bias else None
+        if self.shared_inner:
+            self.shared_up = Linear(tensors[p + "shared.up"])
+            self.shared_down = Linear(tensors[p + "shared.down"])
+            self.shared_gate = tensors[p + "shared.sg"].to(self.router.dtype).reshape(-1).contiguous()
+
+    def own_weights(self):
+        # a step reads the router, the shared expert, and of the routed experts at most what its tokens choose
+        w = [self.router]
+        if self.shared_inner:
+            w += [self.shared_up.weight, self.shared_down.weight]
+        return w
+
+    def weight_bytes(self) -> int:
+        per_expert = (self.up[0].numel() + self.down[0].numel()) * self.up.element_size()
+        return super().weight_bytes() + self.K * per_expert         # one token's worth; a batch reads more experts
+
+    def forward(self, ctx, h, out):
+        n = ctx.n_tokens
+        rt = self.runtime
+        K, E, D = self.K, self.E, self.width
+        pairs = n * K
+        tile = 16 if pairs <= 16 * E else 64
+        max_tiles = ops.moe_max_tiles(pairs, E, tile)
+        rows = max_tiles * tile
+        with ctx.ws.scope():
+            chosen = ctx.ws.alloc((n, K), torch.int32)
+            share = ctx.ws.alloc((n, K), torch.float32)
+            gate = ctx.ws.alloc((n,), torch.float32) if self.shared_inner else None
+            ops.moe_route(h[:n], self.router, self.router_b, self.shared_gate, K, chosen, share, gate)
+            place_token = ctx.ws.alloc((rows,), torch.int32)
+            pair_place = ctx.ws.alloc((pairs,), torch.int32)
+            tile_expert = ctx.ws.alloc((max_tiles,), torch.int32)
+            ops.moe_sort(chosen, E, tile, place_token, pair_place, tile_expert)
+            act = ctx.ws.alloc((rows, self.inner), rt.dtype)
+            ops.grouped_linear(h[:n], place_token, self.up, tile_expert, tile, act, self.activation, ctx)
+            y = ctx.ws.alloc((rows, D), torch.float32)
+            ops.grouped_linear(act, None, self.down, tile_expert, tile, y, None, ctx)
+            shared, shared_parts, shared_stride = None, 1, 0
+            if self.shared_inner:
+                z = ctx.ws.alloc((ctx.max_slabs, n, self.shared_inner), torch.float32)
+                parts = self.shared_up.slabs(ctx, h[:n], z)
+                a = ctx.ws.alloc((n, self.shared_inner), rt.dtype)
+                ops.activation(z[0], a, self.activation, n_partials=parts, partial_stride=z.stride(0))
+                sh = ctx.ws.alloc((ctx.max_slabs, n, D), torch.float32)
+                shared_parts = self.shared_down.slabs(ctx, a, sh)
+                shared, shared_stride = sh[0], sh.stride(0)
+            ops.moe_combine(y, pair_place, share, shared, shared_parts, shared_stride, gate, out, n)
+        ctx.pending_slabs = 1
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

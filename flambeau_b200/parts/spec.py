@@ -50,10 +50,12 @@ class LayerCall:
     mixer writes nothing and reads the cache that the earlier call with that
     index in the order list owns.  `reenter`: before this call the model's re-entry part (ModelSpec.reentry)
     replaces the stream by a map of the stream and of the embedding output (a looped stretch of layers that takes
-    the embedding in again at the start of every pass)."""
+    the embedding in again at the start of every pass); `pass_index` then says which pass of the stretch begins
+    (0, 1, ...), for re-entry parts that treat the passes differently."""
     layer: int
     cache_from: Optional[int] = None
     reenter: bool = False
+    pass_index: int = 0
 
 
 @dataclass
