@@ -20,6 +20,27 @@ import torch
 
 F64 = torch.float64
 
+# How much of a difference is rounding?  With `rounding_to(torch.bfloat16)` active, the values that a bfloat16 engine
+# may keep in 16 bits (normalised rows, q, k, v, the heads' outputs, activations) are rounded to that type on their
+# way; the distance between such a run and the exact one is the noise that rounding alone causes, from which the
+# tests take their bfloat16 tolerance.  Without it nothing is rounded.
+_ROUND = [None]
+
+
+class rounding_to:
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        _ROUND[0] = self.dtype
+
+    def __exit__(self, *exc):
+        _ROUND[0] = None
+
+
+def kept(x):
+    return x if _ROUND[0] is None else x.to(_ROUND[0]).to(F64)
+
 
 # ---- small mechanisms -------------------------------------------------------------------------------------------
 def unit_rms(x, eps):
@@ -89,15 +110,16 @@ def windowed_attention(h, w, p, m, eps):
     k = plain_norm(h @ w[p + "k"].T, w[p + "k.norm"], eps).view(n, G, d)
     v = (h @ w[p + "v"].T).view(n, G, e)
     pos = list(range(n))
-    q = rotate_half(q, pos, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate_half(k, pos, m["rot"]["base"], m["rot"]["dims"])
+    q = kept(rotate_half(q, pos, m["rot"]["base"], m["rot"]["dims"]))
+    k = kept(rotate_half(k, pos, m["rot"]["base"], m["rot"]["dims"]))
+    v = kept(v)
     mask = window_mask(n, m["mask"]["size"])
     heads = []
     for hh in range(H):
         g = hh // (H // G)
         a = sink_softmax((q[:, hh] @ k[:, g].T) * m["scale"], mask, w[p + "sink"][hh])
         heads.append(a @ v[:, g])
-    return torch.cat(heads, dim=-1) @ w[p + "o"].T
+    return kept(torch.cat(heads, dim=-1)) @ w[p + "o"].T
 
 
 # ---- the recurrent side ----------------------------------------------------------------------------------------------
@@ -147,7 +169,7 @@ def gated_delta(h, w, p, m, eps):
         g = hh // (Hr // Gr)
         o = delta_rule(q[:, g], k[:, g], v[:, hh], beta[:, hh], decay[:, hh])
         heads.append(plain_norm(o, w[p + "norm"], eps) * gate[:, hh])
-    return torch.cat(heads, dim=-1) @ w[p + "o"].T
+    return kept(torch.cat(heads, dim=-1)) @ w[p + "o"].T
 
 
 def parallel_mixer(h, w, p, m, eps):
@@ -159,7 +181,7 @@ def parallel_mixer(h, w, p, m, eps):
 
 # ---- the feed-forward ------------------------------------------------------------------------------------------------
 def expert(h, w, p):
-    return relu_squared(h @ w[p + "up"].T) @ w[p + "down"].T
+    return kept(relu_squared(h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
 def routed_experts(h, w, p, mlp):
@@ -196,14 +218,24 @@ def forward(cfg, w, tokens, layer_outputs=None):
     x = x0
     for i, start_of_pass in run_order(cfg):
         if start_of_pass is not None:
-            x = torch.cat([x, x0], dim=-1) @ w["loop.in"].T + w["loop.step"][start_of_pass][None, :]
+            x = kept(torch.cat([x, x0], dim=-1)) @ w["loop.in"].T + w["loop.step"][start_of_pass][None, :]
         L, p = cfg["layers"][i], f"l{i}."
-        x = x + parallel_mixer(offset_norm(x, w[p + "norm1"], eps), w, p + "mix.", L["mixer"], eps)
+        x = x + parallel_mixer(kept(offset_norm(x, w[p + "norm1"], eps)), w, p + "mix.", L["mixer"], eps)
         if L.get("mlp") is not None:
-            x = x + routed_experts(offset_norm(x, w[p + "norm2"], eps), w, p + "mlp.", L["mlp"])
+            x = x + routed_experts(kept(offset_norm(x, w[p + "norm2"], eps)), w, p + "mlp.", L["mlp"])
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
-    return offset_norm(x, w["final.norm"], eps) @ w["head"].T
+    return kept(offset_norm(x, w["final.norm"], eps)) @ w["head"].T
+
+
+def rounding_noise(cfg, w, tokens, dtype=torch.bfloat16):
+    """Per position, the largest difference between the logits with the 16-bit values rounded and the exact ones, as a
+    fraction of the largest exact logit: (the largest over the positions, their median)."""
+    exact = forward(cfg, w, tokens)
+    with rounding_to(dtype):
+        rounded = forward(cfg, w, tokens)
+    per_row = (rounded - exact).abs().max(dim=1).values / exact.abs().max()
+    return float(per_row.max()), float(per_row.median())
 
 
 # ---- a safetensors reader of its own -----------------------------------------------------------------------------------
