@@ -76,7 +76,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TO* __restrict__ out, long ldo, long slab_stride, float* __restrict__ partials,
                int* __restrict__ tile_counters, int M, int N, int K, int splits, int tiles_m, int tiles_n,
-               int n_units, int gated, int* status) {
+               int n_units, int gated, int* status, const int* __restrict__ tile_group, int group_rows,
+               int plain_act) {
+    // Grouped form (tile_group != nullptr): token tile t multiplies with the weight rows of group tile_group[t]
+    // (rows [g * group_rows, g * group_rows + N) of the stacked matrix that map_w covers); a tile whose group is
+    // negative is skipped by all three roles alike.  K is not split there.
     using Cfg = TileCfg<BN>;
     constexpr int S = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -118,8 +122,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (elect_one()) {
             uint32_t it = 0;                     // stages issued so far, over all units
             bool first = true;
+            if (tile_group) {                    // which weights a tile wants is the work of the kernel before this one
+                fb_pdl_wait();
+                first = false;
+            }
             for (int u = blockIdx.x; u < n_units && !*(volatile int*)bail; u += gridDim.x) {
-                const Unit w = unit_of(u, tiles_m, tiles_n, splits, kb_total);
+                Unit w = unit_of(u, tiles_m, tiles_n, splits, kb_total);
+                if (tile_group) {
+                    const int g = tile_group[w.m0];
+                    if (g < 0) continue;
+                    w.n0 += g * group_rows;
+                }
                 const int m0 = w.m0 * BN;
                 int i = 0;
                 if (first) {
@@ -159,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     }
                 }
             }
-            if (first) fb_pdl_wait();
+            if (first && !tile_group) fb_pdl_wait();
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -168,8 +181,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             constexpr uint32_t idesc = umma_idesc(BN);
             uint32_t it = 0;
             int j = 0;                           // units done by this CTA
+            if (tile_group) fb_pdl_wait();
             for (int u = blockIdx.x; u < n_units && !*(volatile int*)bail; u += gridDim.x, ++j) {
                 const Unit w = unit_of(u, tiles_m, tiles_n, splits, kb_total);
+                if (tile_group && tile_group[w.m0] < 0) { --j; continue; }
                 const int b = j & 1;
                 const uint32_t use = (uint32_t)(j >> 1);
                 // the epilogue must have drained this accumulator (two units ago)
@@ -211,6 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int j = 0;
         for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
             const Unit w = unit_of(u, tiles_m, tiles_n, splits, kb_total);
+            if (tile_group && tile_group[w.m0] < 0) { --j; continue; }
             const int m0 = w.m0 * BN, n0 = w.n0, split = w.split, n_kb = w.n_kb;
             const int n = n0 + row_local;
             const int b = j & 1;
@@ -253,7 +269,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         } else if (n < N) {
 #pragma unroll
                             for (int q = 0; q < 16; ++q)
-                                if (m0 + c + q < M) dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(v[q]);
+                                if (m0 + c + q < M)
+                                    dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(fb_plain_act(plain_act, v[q]));
                         }
                     }
                 }
@@ -337,7 +354,8 @@ int pick_splits(int tiles, int kb_total, int slots, int max_splits, double share
 template <int BN, typename TO>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo, long slab_stride, int max_slabs,
               int* splits_used, float* partials, long partial_floats, int* counters, int n_counters, int M, int N,
-              int K, int force_splits, int* status, cudaStream_t stream, int gated = 0) {
+              int K, int force_splits, int* status, cudaStream_t stream, int gated = 0,
+              const int* tile_group = nullptr, int group_rows = 0, int plain_act = 0) {
     using Cfg = TileCfg<BN>;
     const int tiles_n = (N + BM - 1) / BM, tiles_m = (M + BN - 1) / BN;
     const int tiles = tiles_n * tiles_m;
@@ -351,7 +369,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
                                        : 2.0 * BM * BN * BK / FB_MODEL_SM_FLOPS;
     const double share_cost_kb = ((double)M * N * 8.0 / FB_MODEL_HBM_BYTES_PER_S) / kb_seconds;
     int splits = force_splits > 0 ? force_splits : pick_splits(tiles, kb_total, slots, 16, share_cost_kb);
-    if (gated) splits = 1;                       // the activation needs the whole sum
+    if (gated || tile_group) splits = 1;         // the activation needs the whole sum; grouped tiles are not split
     if (splits > kb_total) splits = kb_total;
     if (slab_stride > 0) {
         if (splits > max_slabs) splits = max_slabs;
@@ -371,7 +389,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     }
     const int grid = (int)(n_units < slots ? n_units : slots);
     fb_launch_class(BN >= 256 ? FB_LAUNCH_GEMM_WIDE : FB_LAUNCH_OTHER, (kern), grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream, mw, mx, (TO*)out, ldo, slab_stride, partials,
-              counters, M, N, K, splits, tiles_m, tiles_n, (int)n_units, gated, status);
+              counters, M, N, K, splits, tiles_m, tiles_n, (int)n_units, gated, status, tile_group, group_rows, plain_act);
     return fb_check_launch("gemm_tc");
 }
 
@@ -430,6 +448,45 @@ FB_API int fb_gemm_tc(const void* X, long long lda, const void* W, long long ldw
     }
 #undef FB_TC_CASE
     return fb_fail(-1, "gemm_tc: unknown output dtype code %d", o_dtype);
+}
+
+// The grouped form: out[m] = act(X[m] * W[g]^T) with g = tile_group[m / tile] and W [groups, N, K] contiguous; the M
+// rows come in whole tiles of `tile` (16, 32, 64 or 128) rows, each of one group (negative: skipped, its rows are
+// left as they are).  `act` is an FbPlainAct code.  For the products of routed experts over tokens sorted by expert.
+FB_API int fb_gemm_tc_grouped(const void* X, long long lda, const void* W, long long ldw, int groups,
+                              const int* tile_group, int tile, void* out, int o_dtype, long long ldo, int M, int N,
+                              int K, int act, int* status, cudaStream_t stream) {
+    FB_REQUIRE(M >= 0 && N > 0 && K > 0 && groups > 0, "gemm_tc_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
+    FB_REQUIRE(tile == 16 || tile == 32 || tile == 64 || tile == 128, "gemm_tc_grouped: row tiles of 16 to 128, not %d", tile);
+    FB_REQUIRE(M % tile == 0 && tile_group, "gemm_tc_grouped: the rows must be whole tiles with a group each");
+    FB_REQUIRE(lda >= K && ldw >= K && ldo >= N, "gemm_tc_grouped: a row stride is shorter than its row");
+    FB_REQUIRE(lda % 8 == 0 && ldw % 8 == 0, "gemm_tc_grouped: row strides must be multiples of 8 elements");
+    FB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc_grouped: operands must be 16-byte aligned");
+    FB_REQUIRE(fb_plain_act_known(act), "gemm_tc_grouped: unknown activation code %d", act);
+    FB_REQUIRE((long long)groups * N < 2147483647LL, "gemm_tc_grouped: too many weight rows");
+    if (M == 0) return 0;
+    CUtensorMap mw, mx;
+    int rc = fb_tensor_map_bf16(&mw, W, (long long)groups * N, K, (long)ldw, BK, BM);
+    if (rc) return rc;
+    rc = fb_tensor_map_bf16(&mx, X, M, K, (long)lda, BK, tile);
+    if (rc) return rc;
+#define FB_TCGR_CASE(BN_)                                                                                       \
+    case BN_:                                                                                                   \
+        if (o_dtype == FB_F32)                                                                                  \
+            return launch_tc<BN_, float>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, M, N, K, \
+                                         1, status, stream, 0, tile_group, N, act);                             \
+        else if (o_dtype == FB_BF16)                                                                            \
+            return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, \
+                                                 M, N, K, 1, status, stream, 0, tile_group, N, act);            \
+        break;
+    switch (tile) {
+        FB_TCGR_CASE(16)
+        FB_TCGR_CASE(32)
+        FB_TCGR_CASE(64)
+        FB_TCGR_CASE(128)
+    }
+#undef FB_TCGR_CASE
+    return fb_fail(-1, "gemm_tc_grouped: unknown output dtype code %d", o_dtype);
 }
 
 // acc[M,N] += X[M,K] * W[N,K]^T in float32 where the product is one that leaves in whole tiles through the two-SM

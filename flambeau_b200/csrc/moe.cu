@@ -128,6 +128,38 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, long ex
     out[idx] = acc;
 }
 
+// out[place] = h[place_token[place]] (a row of zeros where the place is padding): the tokens side by side in expert
+// order, for the products that fetch their rows by tensor-map copies.
+template <typename T>
+__global__ void moe_gather_rows_kernel(const T* __restrict__ h, long h_stride, const int* __restrict__ place_token,
+                                       T* __restrict__ out, int rows, int D) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int chunks = D / 8;                          // 16 bytes of bfloat16, 32 of float32
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * chunks) return;
+    const int r = (int)(idx / chunks), c = (int)(idx - (size_t)r * chunks);
+    const int src = place_token[r];
+    struct alignas(sizeof(T) * 8) Chunk { T v[8]; };
+    Chunk z;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) z.v[i] = fb_from_float<T>(0.0f);
+    if (src >= 0) z = *reinterpret_cast<const Chunk*>(h + (size_t)src * h_stride + (size_t)c * 8);
+    *reinterpret_cast<Chunk*>(out + (size_t)r * D + (size_t)c * 8) = z;
+}
+
+FB_API int fb_moe_gather_rows(const void* h, long long h_stride, int dtype, const int* place_token, void* out,
+                              int rows, int D, cudaStream_t stream) {
+    FB_REQUIRE(rows >= 0 && D > 0 && D % 8 == 0 && h_stride % 8 == 0, "moe_gather_rows: widths must be multiples of 8");
+    FB_REQUIRE(((uintptr_t)h & 31) == 0 && ((uintptr_t)out & 31) == 0, "moe_gather_rows: rows must be 32-byte aligned");
+    if (rows == 0) return 0;
+    const size_t total = (size_t)rows * (D / 8);
+    FB_DISPATCH_DTYPE(dtype, T,
+        (fb_launch((moe_gather_rows_kernel<T>), dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                   (const T*)h, (long)h_stride, place_token, (T*)out, rows, D)));
+    return fb_check_launch("moe_gather_rows");
+}
+
 FB_API int fb_moe_route(const void* h, long long h_stride, int h_dtype, const void* wr, const void* br,
                         const void* w_gate, int w_dtype, int n, int D, int E, int K, int* chosen, float* share,
                         float* gate, cudaStream_t stream) {

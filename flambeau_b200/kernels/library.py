@@ -43,6 +43,7 @@ _SIGNATURES = {
     # gemm_tc.cu
     "fb_gemm_tc_add": (I, [P, L, P, L, P, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc": (I, [P, L, P, L, P, I, L, L, I, P, I, I, I, P, L, P, I, I, P, STREAM]),
+    "fb_gemm_tc_grouped": (I, [P, L, P, L, I, P, I, P, I, L, I, I, I, I, P, STREAM]),
     "fb_gemm_tc_gated": (I, [P, L, P, L, P, I, L, I, I, I, I, P, L, P, I, P, STREAM]),
     # attention_simt.cu
     "fb_paged_attention_simt": (I, [P, L, P, L, I, P, P, I, I, P, I, P, P, P, I, I, I, I, I, I, F, P, P, P, STREAM]),
@@ -56,6 +57,7 @@ _SIGNATURES = {
     # moe.cu
     "fb_moe_route": (I, [P, L, I, P, P, P, I, I, I, I, I, P, P, P, STREAM]),
     "fb_moe_max_tiles": (I, [I, I, I]),
+    "fb_moe_gather_rows": (I, [P, L, I, P, P, I, I, STREAM]),
     "fb_moe_sort": (I, [P, I, I, I, I, I, P, P, P, STREAM]),
     "fb_moe_combine": (I, [P, L, P, P, I, P, I, L, P, P, I, I, STREAM]),
     # diff_attention.cu

@@ -529,10 +529,71 @@ def linear_slabs(a: torch.Tensor, w: torch.Tensor, slabs: torch.Tensor, ctx) -> 
     return 1
 
 
+def grouped_tc_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel takes a grouped product: bfloat16 operands whose rows TMA can fetch."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.float32, torch.bfloat16)
+            and a.dim() == 2 and a.stride(1) == 1 and a.stride(0) % 8 == 0 and w.shape[-1] % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous()
+            and _GROUPED_TC[0])
+
+
+_GROUPED_TC = [os.environ.get("FLAMBEAU_MOE_TC", "1") != "0"]
+
+
+def grouped_tile(pairs: int, groups: int, tensor_cores: bool) -> int:
+    """Rows of a tile of the grouped products for `pairs` rows spread over `groups` groups: small tiles while a
+    group holds few rows (decoding: a tile of 16 streams an expert's weights once), larger ones as the groups fill
+    (128 on the tensor cores, whose instruction takes as long for 64 columns as for 128)."""
+    if pairs <= 16 * groups:
+        return 16
+    if tensor_cores and pairs >= 192 * groups:
+        return 128
+    return 64
+
+
+def gather_rows(h: torch.Tensor, place_token: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i] = h[place_token[i]], zeros where place_token[i] < 0."""
+    _cuda(h, place_token, out)
+    _i32(place_token, "place_token")
+    rows, D = out.shape
+    if h.dtype != out.dtype or h.shape[1] != D or not out.is_contiguous() or place_token.numel() < rows:
+        raise KernelError("gather_rows: shapes or dtypes do not agree")
+    check(lib().fb_moe_gather_rows(h.data_ptr(), _rows(h), dtype_code(h), place_token.data_ptr(), out.data_ptr(), rows,
+                                   D, _stream()), "moe_gather_rows")
+
+
+def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, tile: int, out: torch.Tensor,
+                    status: torch.Tensor, activation_name=None) -> None:
+    """out[m] = act(a[m] @ w[tile_group[m // tile]]^T) on the tcgen05 kernel; a [M, K] with M whole tiles."""
+    _cuda(a, w, tile_group, out, status)
+    _i32(tile_group, "tile_group")
+    groups, N, K = w.shape
+    M = out.shape[0]
+    if a.shape[0] != M or a.shape[1] != K or out.shape[1] != N or tile_group.numel() * tile < M:
+        raise KernelError("grouped gemm: shapes do not agree")
+    check(lib().fb_gemm_tc_grouped(a.data_ptr(), _rows(a), w.data_ptr(), K, groups, tile_group.data_ptr(), int(tile),
+                                   out.data_ptr(), dtype_code(out), _rows(out), M, N, K,
+                                   plain_activation_code(activation_name), status.data_ptr(), _stream()),
+          "gemm_tc_grouped", (M, N, K))
+
+
 def grouped_linear(a: torch.Tensor, row_index, w: torch.Tensor, tile_group: torch.Tensor, tile: int,
                    out: torch.Tensor, activation_name=None, ctx=None) -> None:
     """out[m] = act(a[row_index[m]] @ w[tile_group[m // tile]]^T) with w [groups, N, K]: the product of routed
-    experts over rows that were sorted by expert and padded to whole tiles (see gemm_simt_grouped)."""
+    experts over rows that were sorted by expert and padded to whole tiles.  bfloat16 operands go to the tcgen05
+    kernel (rows that have to be fetched through row_index are first laid side by side, since tensor-map copies
+    take whole tiles of consecutive rows); everything else to the float32-FMA kernel, which fetches by index."""
+    if ctx is not None and grouped_tc_supported(a, w, out):
+        if row_index is not None:
+            with ctx.ws.scope():
+                side = ctx.ws.alloc((out.shape[0], a.shape[1]), a.dtype)
+                gather_rows(a, row_index, side)
+                gemm_tc_grouped(side, w, tile_group, tile, out, ctx.runtime.status, activation_name)
+        else:
+            gemm_tc_grouped(a, w, tile_group, tile, out, ctx.runtime.status, activation_name)
+        return
+    if tile not in (16, 64):
+        raise KernelError(f"grouped gemm: the float32-FMA kernel takes tiles of 16 or 64 rows, not {tile}")
     gemm_simt_grouped(a, row_index, w, tile_group, tile, out, activation_name)
 
 

@@ -84,7 +84,9 @@ class RoutedExperts(FeedForward):
         rt = self.runtime
         K, E, D = self.K, self.E, self.width
         pairs = n * K
-        tile = 16 if pairs <= 16 * E else 64
+        # (the second product's rows are the first one's output, whose width must suit the tensor cores too)
+        on_tc = ops.grouped_tc_supported(h, self.up, h) and self.inner % 8 == 0
+        tile = ops.grouped_tile(pairs, E, on_tc)
         max_tiles = ops.moe_max_tiles(pairs, E, tile)
         rows = max_tiles * tile
         with ctx.ws.scope():
