@@ -47,6 +47,8 @@ struct AttnArgs {
     const float* score_slopes;         // per query head, or nullptr: slope * (key position - query position) is added
                                        // to the scaled score (a linear penalty on distance; <= 0 for the keys a
                                        // query sees when the slope is >= 0)
+    const float* sinks;                // per query head, or nullptr: one more softmax slot whose score is this number as it
+                                       // stands (not scaled), without key or value; it joins the denominator once
     float* part_o; float* part_ml;     // split-key: partial results, [slot][16 rows][HD_MAX] and [slot][16][2]
     int* part_cnt;                     // split-key: per (sequence, key/value head), segments that have arrived; 0 at rest
     int n_seqs;                        // sequences of the step
@@ -56,6 +58,11 @@ struct AttnArgs {
     FbPrefetch prefetch;               // split-key: rows to fetch into L2 when a CTA has issued its last tile
     int* status;
 };
+
+// What a head's sink adds to a row's denominator whose terms are 2^(score - m), scores in base-2 units.
+__device__ __forceinline__ float sink_term(const AttnArgs& a, int head, float m) {
+    return (a.sinks && m > -INFINITY) ? exp2f(a.sinks[head] * 1.4426950408889634f - m) : 0.0f;
+}
 
 // The page id of logical page `logical` of a sequence whose table row `table` starts at logical page `base_page`
 // (-1 where the row has no such column).

@@ -359,8 +359,9 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         for (int h = 0; h < 2; ++h) {
             const int r = row_base + 16 * rb + (lane >> 2) + 8 * h;
             if (r >= rows_valid) continue;
-            const float inv = l_run[rb][h] > 0.0f ? 1.0f / l_run[rb][h] : 0.0f;
             const int token = q_start + tok0 + r / G, head = kvh * G + r % G;
+            const float l_all = l_run[rb][h] + sink_term(a, head, m_run[rb][h]);
+            const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
             __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
 #pragma unroll
             for (int d = 0; d < NDB; ++d) {
@@ -435,7 +436,8 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
                                   const int* block_table, int table_stride, const int* table_base,
                                   const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start,
                                   const int* multi_seqs, int n_multi, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
-                                  int window, float scale, const float* score_slopes, float* scratch,
+                                  int window, float scale, const float* score_slopes, const float* sinks,
+                                  float* scratch,
                                   long long scratch_floats,
                                   const void* prefetch_base, long long prefetch_rows, long long prefetch_row_stride,
                                   int prefetch_bytes_per_row, int* status, cudaStream_t stream) {
@@ -461,6 +463,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f;
     a.score_slopes = score_slopes;
+    a.sinks = sinks;
     a.status = status;
     a.short_rows = G <= 16 ? 16 : 0;               // with more than 16 heads per group even one token is "long"
     if (a.short_rows == 0) {                       // then single tokens run in the arrangement for portions as well,

@@ -85,7 +85,7 @@ __device__ __forceinline__ void short_prefix(const AttnArgs& a, int G, const Sho
 // of the head's columns.  The partials were written by other SMs: they are read past the L1.
 template <int HD_MAX>
 __device__ __forceinline__ void merge_row(const AttnArgs& a, size_t slot0, int n_chunks, int r, int lane,
-                                          __nv_bfloat16* dst) {
+                                          __nv_bfloat16* dst, int head) {
     constexpr int U = HD_MAX <= 128 ? 16 : 8;          // partials whose loads are in flight together
     float acc[HD_MAX / 32];
 #pragma unroll
@@ -124,7 +124,7 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, size_t slot0, int n
             }
         }
     }
-    l = fb_warp_sum(l);
+    l = fb_warp_sum(l) + sink_term(a, head, m);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
     for (int i = 0; i < HD_MAX / 32; ++i) {
@@ -555,8 +555,9 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                         if ((lane & 3) == 0)
                             *reinterpret_cast<float2*>(a.part_ml + (slot * 16 + r) * 2) = make_float2(m_all[h], l_all[h]);
                     } else {                          // the whole pair was this CTA's: the result itself
-                        const float inv = l_all[h] > 0.0f ? 1.0f / l_all[h] : 0.0f;
                         const int token = q_start + r / G, head = kvh * G + r % G;
+                        const float l_sink = l_all[h] + sink_term(a, head, m_all[h]);
+                        const float inv = l_sink > 0.0f ? 1.0f / l_sink : 0.0f;
                         __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd + 2 * (lane & 3);
 #pragma unroll
                         for (int d = 0; d < NDB; ++d) {
@@ -584,7 +585,7 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                 for (int r = warp; r < rows_valid; r += SPLIT_SCORERS) {
                     const int token = q_start + r / G, head = kvh * G + r % G;
                     merge_row<HD_MAX>(a, slot0, cur.n_chunks, r, lane,
-                                      a.out + (size_t)token * a.out_stride + (size_t)head * hd);
+                                      a.out + (size_t)token * a.out_stride + (size_t)head * hd, head);
                 }
             }
         }

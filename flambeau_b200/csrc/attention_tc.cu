@@ -392,6 +392,7 @@ attention_tc_kernel(const __grid_constant__ AttnArgs a) {
         if (ok) ok = __all_sync(0xffffffffu, wait(&o_done[t], 0));
         if (ok) {
             tmem_fence_after();
+            l += sink_term(a, head, m_ref);
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = a.out + (size_t)token * a.out_stride + (size_t)head * hd;
 #pragma unroll

@@ -156,8 +156,9 @@ class PagedAttention(Mixer):
                     pos.half if pos is not None else 0, q, cache, ctx.batch.positions, ctx.batch.row_seq, self.nh,
                     self.nkv, self.hd, self.vd, rt.status, n_partials=parts, partial_stride=slabs.stride(0))
                 a = ctx.ws.alloc((n, self.nh * self.vd), rt.dtype)
+                hint = self.o.weight if ctx.l2_hints and n <= 64 else None
                 ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
-                                    score_slopes=self.distance_slopes, sinks=self.sinks, vd=self.vd)
+                                    next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks, vd=self.vd)
                 ctx.to_stream(self.o, a)
                 return
             if self.vd != self.hd or self.qk_norm_reach != "head":
