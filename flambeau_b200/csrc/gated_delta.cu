@@ -7,15 +7,19 @@
 // request's tokens are taken in order; nothing but q, k, g and beta is shared between columns.
 //
 // Kernels, in the order a step runs them:
-//   gdr_prepare      per token: add the projection's split-K shares, the short causal convolution over time with its
-//                    SiLU on the q, k and v channels (inputs before the portion's start come from the request's
-//                    kept tail), q and k made unit vectors per head (q also times `q_scale`), beta = sigmoid,
+//   gdr_prepare      per (token, head of q, k or v): add the projection's split-K shares, the short causal convolution
+//                    over time with its SiLU (inputs before the portion's start come from the request's kept tail),
+//                    q and k made unit vectors per head (q also times `q_scale`), beta = sigmoid,
 //                    g = exp(-exp(A_log) * softplus(a + dt_bias)); all float32
 //   gdr_conv_tail    per request: the last taps-1 convolution inputs of the step become the kept tail
-//   gdr_recurrent    per (request, head, slice of columns): the recurrence over the step's tokens, state in registers
+//   gdr_recurrent    per (request, head, 16 columns): the recurrence over the step's tokens, state in registers, sixteen
+//                    lanes a column.  Both products with the state are taken from the state before the token's
+//                    update, a = S^T k and b = S^T q, so that they share one exchange between the lanes:
+//                    u = beta (v - g a), o = g b + u (k . q), S <- g S + k u^T, which is the same arithmetic
 //   gdr_out_norm     per (token, head): o / rms(o) * weight * silu(gate), rounded to the engine's dtype
 //
-// A request's slot of state is one float32 array: S as [heads][dk][dv], then the tail as [taps-1][channels]
+// A request's slot of state is one float32 array: S as [heads][dv][dk] (a column's dk values side by side), then the
+// tail as [taps-1][channels]
 // (oldest first).  Projection rows are [q: G*dk | k: G*dk | v: H*dv | b: H | a: H | gate: H*dv]; head h of H reads
 // q/k head h / (H / G).
 #include "common.cuh"
@@ -29,7 +33,7 @@ __device__ __forceinline__ float gdr_silu(float z) { return z / (1.0f + expf(-z)
 __device__ __forceinline__ float gdr_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
 template <typename TW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 gdr_prepare_kernel(const float* __restrict__ proj, long proj_stride, int n_partials, long partial_stride,
                    const TW* __restrict__ conv_w, int taps, const TW* __restrict__ a_log, const TW* __restrict__ dt_bias,
                    const float* __restrict__ state, long state_stride, long tail_off, const int* __restrict__ row_seq,
@@ -38,14 +42,24 @@ gdr_prepare_kernel(const float* __restrict__ proj, long proj_stride, int n_parti
                    float unit_eps) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
-    extern __shared__ float sh[];                      // [2 * G * dk] q and k channels after convolution and SiLU
-    const int row = blockIdx.x, tid = threadIdx.x;
+    constexpr int PER = 8;                             // channels a thread takes: heads of up to 1024
+    __shared__ float red[32];
+    const int row = blockIdx.x, unit = blockIdx.y, tid = threadIdx.x;
     const int qk = G * dk, C = 2 * qk + H * dv;
+    const bool is_v = unit >= 2 * G;
+    const int width = is_v ? dv : dk;
+    const int base = is_v ? 2 * qk + (unit - 2 * G) * dv : unit * dk;    // q heads, then k heads, then v heads
     const int seq = row_seq[row];
     const int i = row - seq_q_start[seq];              // place within the step's portion of this request
     const float* tail = state + (size_t)seq_slot[seq] * state_stride + tail_off;
-    float* out = qkv + (size_t)row * C;
-    for (int c = tid; c < C; c += blockDim.x) {
+    float y[PER];
+    float sq = 0.0f;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int d = tid + 128 * e;
+        y[e] = 0.0f;
+        if (d >= width) continue;
+        const int c = base + d;
         float acc = 0.0f;
         for (int j = 0; j < taps; ++j) {
             const int src = i - (taps - 1 - j);
@@ -54,21 +68,23 @@ gdr_prepare_kernel(const float* __restrict__ proj, long proj_stride, int n_parti
                 : tail[(size_t)(taps - 1 + src) * C + c];
             acc = fmaf(fb_to_float(conv_w[(size_t)c * taps + j]), x, acc);
         }
-        const float y = gdr_silu(acc);
-        if (c < 2 * qk) sh[c] = y; else out[c] = y;
+        y[e] = gdr_silu(acc);
+        sq = fmaf(y[e], y[e], sq);
     }
-    __syncthreads();
-    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-    for (int h = warp; h < 2 * G; h += nwarps) {       // q heads, then k heads
-        const float* x = sh + (size_t)h * dk;
-        float s = 0.0f;
-        for (int d = lane; d < dk; d += 32) s = fmaf(x[d], x[d], s);
-        s = fb_warp_sum(s);
-        const float f = (h < G ? q_scale : 1.0f) / sqrtf(s + unit_eps);
-        for (int d = lane; d < dk; d += 32) out[(size_t)h * dk + d] = x[d] * f;
+    float f = 1.0f;
+    if (!is_v) {                                       // block-uniform
+        sq = fb_block_sum(sq, red);
+        f = (unit < G ? q_scale : 1.0f) / sqrtf(sq + unit_eps);
     }
-    const float* pr = proj + (size_t)row * proj_stride;
-    for (int h = tid; h < H; h += blockDim.x) {
+    float* out = qkv + (size_t)row * C + base;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int d = tid + 128 * e;
+        if (d < width) out[d] = y[e] * f;
+    }
+    if (is_v && tid == 0) {
+        const int h = unit - 2 * G;
+        const float* pr = proj + (size_t)row * proj_stride;
         const float b = gdr_slab_sum(pr, C + h, n_partials, partial_stride);
         const float a = gdr_slab_sum(pr, C + H + h, n_partials, partial_stride);
         beta[(size_t)row * H + h] = 1.0f / (1.0f + expf(-b));
@@ -96,8 +112,8 @@ __global__ void gdr_conv_tail_kernel(const float* __restrict__ proj, long proj_s
     }
 }
 
-// R state values a lane, LPC lanes a column (the key dimension d = lane + LPC * r), 256 / LPC columns a CTA.
-template <int R, int LPC>
+// Sixteen lanes a column, R state values a lane (the key dimension d = lane + 16 r, dk <= 16 R), 16 columns a CTA.
+template <int R>
 __global__ void __launch_bounds__(256)
 gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                      float* __restrict__ state, long state_stride, const int* __restrict__ seq_q_start,
@@ -105,38 +121,39 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
                      int G, int H, int dk, int dv) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
-    constexpr int COLS = 256 / LPC, CH = 16;           // columns of this CTA; tokens fetched at a time
+    constexpr int LPC = 16, COLS = 16, CH = 16, DKP = LPC * R;   // tokens fetched at a time; a key row padded with zeros
     extern __shared__ float sh[];
-    float* qs = sh;                                    // [CH][dk]
-    float* ks = qs + CH * dk;                          // [CH][dk]
-    float* vs = ks + CH * dk;                          // [CH][COLS]
+    float* qs = sh;                                    // [CH][DKP]
+    float* ks = qs + CH * DKP;                         // [CH][DKP]
+    float* vs = ks + CH * DKP;                         // [CH][COLS]
     float* bs = vs + CH * COLS;                        // [CH] beta
     float* gs = bs + CH;                               // [CH] decay
+    float* kq = gs + CH;                               // [CH] k . q
     const int seq = blockIdx.x / H, head = blockIdx.x - seq * H;
     const int g = head / (H / G);
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int li = tid % LPC, col = blockIdx.y * COLS + tid / LPC;
     const bool live = col < dv;
     const int qk = G * dk, C = 2 * qk + H * dv;
     const int start = seq_q_start[seq], L = seq_q_len[seq];
-    float* S = state + (size_t)seq_slot[seq] * state_stride + (size_t)head * dk * dv;
+    float* S = state + (size_t)seq_slot[seq] * state_stride + ((size_t)head * dv + (live ? col : 0)) * dk;
     float s[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = li + LPC * r;
-        s[r] = (live && d < dk) ? S[(size_t)d * dv + col] : 0.0f;
+        s[r] = (live && d < dk) ? S[d] : 0.0f;
     }
     for (int t0 = 0; t0 < L; t0 += CH) {
         const int cnt = min(CH, L - t0);
         __syncthreads();
-        for (int e = tid; e < cnt * dk; e += 256) {
-            const int t = e / dk, d = e - t * dk;
-            const float* rowp = qkv + (size_t)(start + t0 + t) * C;
-            qs[e] = rowp[(size_t)g * dk + d];
-            ks[e] = rowp[qk + (size_t)g * dk + d];
+        for (int e = tid; e < cnt * DKP; e += 256) {
+            const int t = e / DKP, d = e - t * DKP;
+            const float* rowp = qkv + (size_t)(start + t0 + t) * C + (size_t)g * dk;
+            qs[e] = d < dk ? rowp[d] : 0.0f;
+            ks[e] = d < dk ? rowp[qk + d] : 0.0f;
         }
         for (int e = tid; e < cnt * COLS; e += 256) {
-            const int t = e / COLS, cc = e - t * COLS, c2 = blockIdx.y * COLS + cc;
+            const int t = e / COLS, c2 = blockIdx.y * COLS + (e - t * COLS);
             vs[e] = c2 < dv ? qkv[(size_t)(start + t0 + t) * C + 2 * qk + (size_t)head * dv + c2] : 0.0f;
         }
         if (tid < cnt) {
@@ -144,38 +161,43 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
             gs[tid] = decay[(size_t)(start + t0 + tid) * H + head];
         }
         __syncthreads();
+        for (int t = warp; t < cnt; t += 8) {
+            float acc = 0.0f;
+            for (int d = lane; d < DKP; d += 32) acc = fmaf(ks[t * DKP + d], qs[t * DKP + d], acc);
+            acc = fb_warp_sum(acc);
+            if (lane == 0) kq[t] = acc;
+        }
+        __syncthreads();
         for (int t = 0; t < cnt; ++t) {
             const float gt = gs[t], bt = bs[t];
-            const float* kt = ks + t * dk;
-            const float* qt = qs + t * dk;
-            float dot = 0.0f;
+            const float* kt = ks + t * DKP + li;
+            const float* qt = qs + t * DKP + li;
+            float kk[R];
+            float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const int d = li + LPC * r;
-                s[r] *= gt;
-                if (d < dk) dot = fmaf(s[r], kt[d], dot);
+                kk[r] = kt[LPC * r];
+                const float qq = qt[LPC * r];
+                if (r & 1) { a1 = fmaf(s[r], kk[r], a1); b1 = fmaf(s[r], qq, b1); }
+                else { a0 = fmaf(s[r], kk[r], a0); b0 = fmaf(s[r], qq, b0); }
             }
+            float a = a0 + a1, b = b0 + b1;
 #pragma unroll
-            for (int off = LPC / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-            const float u = bt * (vs[t * COLS + tid / LPC] - dot);
-            float rd = 0.0f;
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int d = li + LPC * r;
-                if (d < dk) {
-                    s[r] = fmaf(kt[d], u, s[r]);
-                    rd = fmaf(s[r], qt[d], rd);
-                }
+            for (int off = LPC / 2; off > 0; off >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, off);
+                b += __shfl_xor_sync(0xffffffffu, b, off);
             }
+            const float u = bt * (vs[t * COLS + tid / LPC] - gt * a);
 #pragma unroll
-            for (int off = LPC / 2; off > 0; off >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, off);
-            if (live && li == 0) o[(size_t)(start + t0 + t) * H * dv + (size_t)head * dv + col] = rd;
+            for (int r = 0; r < R; ++r) s[r] = fmaf(kk[r], u, gt * s[r]);
+            if (live && li == 0)
+                o[(size_t)(start + t0 + t) * H * dv + (size_t)head * dv + col] = fmaf(u, kq[t], gt * b);
         }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = li + LPC * r;
-        if (live && d < dk) S[(size_t)d * dv + col] = s[r];
+        if (live && d < dk) S[d] = s[r];
     }
 }
 
@@ -214,12 +236,11 @@ FB_API int fb_gdr_prepare(const float* proj, long long proj_stride, int n_partia
     FB_REQUIRE(proj_stride >= C + 2LL * H + (long long)H * dv, "gated delta: projection rows are too short");
     if (n == 0) return 0;
     if (n_partials < 1) n_partials = 1;
-    const size_t smem = (size_t)2 * G * dk * sizeof(float);
-    FB_REQUIRE(smem <= 200 * 1024, "gated delta: q and k of a token (%zu bytes) do not fit shared memory", smem);
+    FB_REQUIRE(dk <= 1024 && dv <= 1024, "gated delta: head sizes up to 1024 (key %d, value %d)", dk, dv);
+    FB_REQUIRE(2 * G + H <= 65535, "gated delta: too many heads");
     FB_DISPATCH_DTYPE(w_dtype, TW, {
         auto kernel = gdr_prepare_kernel<TW>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        fb_launch(kernel, dim3(n), dim3(256), smem, stream, proj, (long)proj_stride, n_partials, (long)partial_stride,
+        fb_launch(kernel, dim3(n, 2 * G + H), dim3(128), 0, stream, proj, (long)proj_stride, n_partials, (long)partial_stride,
                   (const TW*)conv_w, taps, (const TW*)a_log, (const TW*)dt_bias, (const float*)state, (long)state_stride,
                   (long)tail_off, row_seq, seq_q_start, seq_slot, qkv, beta, decay, G, H, dk, dv, q_scale, unit_eps);
     });
@@ -231,13 +252,13 @@ FB_API int fb_gdr_prepare(const float* proj, long long proj_stride, int n_partia
     return fb_check_launch("gdr_conv_tail");
 }
 
-template <int R, int LPC>
+template <int R>
 static int launch_gdr_recurrent(const float* qkv, const float* beta, const float* decay, float* state,
                                 long state_stride, const int* seq_q_start, const int* seq_q_len, const int* seq_slot,
                                 int n_seqs, float* o, int G, int H, int dk, int dv, cudaStream_t stream) {
-    constexpr int COLS = 256 / LPC, CH = 16;
-    const size_t smem = ((size_t)2 * CH * dk + CH * COLS + 2 * CH) * sizeof(float);
-    auto kernel = gdr_recurrent_kernel<R, LPC>;
+    constexpr int COLS = 16, CH = 16, DKP = 16 * R;
+    const size_t smem = ((size_t)2 * CH * DKP + CH * COLS + 3 * CH) * sizeof(float);
+    auto kernel = gdr_recurrent_kernel<R>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     fb_launch(kernel, dim3(n_seqs * H, (dv + COLS - 1) / COLS), dim3(256), smem, stream, qkv, beta, decay, state,
               state_stride, seq_q_start, seq_q_len, seq_slot, o, G, H, dk, dv);
@@ -250,14 +271,15 @@ FB_API int fb_gdr_recurrent(const float* qkv, const float* beta, const float* de
     FB_REQUIRE(n_seqs >= 0 && G > 0 && H > 0 && H % G == 0 && dk > 0 && dv > 0, "gated delta: bad sizes");
     FB_REQUIRE(dk <= 1024, "gated delta: key size %d is larger than 1024", dk);
     if (n_seqs == 0) return 0;
-#define FB_GDR_CASE(R, LPC) return launch_gdr_recurrent<R, LPC>(qkv, beta, decay, state, (long)state_stride, \
-        seq_q_start, seq_q_len, seq_slot, n_seqs, o, G, H, dk, dv, stream)
-    if (dk <= 32) FB_GDR_CASE(8, 4);
-    if (dk <= 64) FB_GDR_CASE(16, 4);
-    if (dk <= 128) FB_GDR_CASE(32, 4);
-    if (dk <= 256) FB_GDR_CASE(32, 8);
-    if (dk <= 512) FB_GDR_CASE(32, 16);
-    FB_GDR_CASE(32, 32);
+#define FB_GDR_CASE(R) return launch_gdr_recurrent<R>(qkv, beta, decay, state, (long)state_stride, seq_q_start, \
+        seq_q_len, seq_slot, n_seqs, o, G, H, dk, dv, stream)
+    if (dk <= 16) FB_GDR_CASE(1);
+    if (dk <= 32) FB_GDR_CASE(2);
+    if (dk <= 64) FB_GDR_CASE(4);
+    if (dk <= 128) FB_GDR_CASE(8);
+    if (dk <= 256) FB_GDR_CASE(16);
+    if (dk <= 512) FB_GDR_CASE(32);
+    FB_GDR_CASE(64);
 #undef FB_GDR_CASE
 }
 

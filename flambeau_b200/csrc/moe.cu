@@ -1,9 +1,10 @@
 // Routed experts: which experts a token uses, the order that puts every expert's tokens side by side for the
 // grouped products, and the weighted sum that brings the experts' outputs back to the tokens.
 //
-//   moe_route    per token (one warp): router logits z = Wr h + b in float32, the `top` largest (the lower index wins a
-//                tie), their weights = softmax over the chosen logits only; optionally one more number per token,
-//                sigmoid(w_gate . h), for a shared expert
+//   moe_choose   per token (one warp): the router's logits (a product of the token rows with the router matrix, summed
+//                in float32) plus the bias, the `top` largest (the lower index wins a tie), their weights = softmax
+//                over the chosen logits only; optionally one more number per token, sigmoid of one more column of
+//                that product (w_gate . h), for a shared expert
 //   moe_sort     one CTA: (token, choice) pairs counted per expert, every expert's stretch padded to a multiple of
 //                the products' row tile, so that a row tile belongs to one expert; writes for every place of the
 //                padded order its token (-1: padding), for every pair its place, for every row tile its expert
@@ -13,35 +14,29 @@
 
 constexpr int MOE_MAX_LOGITS_PER_LANE = 16;            // 512 experts at most
 
-template <typename T, typename TW>
+template <typename TW>
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const T* __restrict__ h, long h_stride, const TW* __restrict__ wr, const TW* __restrict__ br,
-                 const TW* __restrict__ w_gate, int n, int D, int E, int K, int* __restrict__ chosen,
-                 float* __restrict__ share, float* __restrict__ gate) {
+moe_choose_kernel(const float* __restrict__ z_in, long z_stride, int n_partials, long partial_stride,
+                  const TW* __restrict__ br, int gate_col, int n, int E, int K, int* __restrict__ chosen,
+                  float* __restrict__ share, float* __restrict__ gate) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;
     if (row >= n) return;
-    const T* x = h + (size_t)row * h_stride;
+    const float* zr = z_in + (size_t)row * z_stride;
+    auto logit = [&](int c) {
+        float v = zr[c];
+        for (int p = 1; p < n_partials; ++p) v += zr[(size_t)p * partial_stride + c];
+        return v;
+    };
     float z[MOE_MAX_LOGITS_PER_LANE];                  // lane l keeps the logits of experts l, l + 32, ...
 #pragma unroll
-    for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) z[r] = -INFINITY;
-    for (int e = 0; e < E; ++e) {
-        const TW* w = wr + (size_t)e * D;
-        float acc = 0.0f;
-        for (int d = lane; d < D; d += 32) acc = fmaf(fb_to_float(x[d]), fb_to_float(w[d]), acc);
-        acc = fb_warp_sum(acc) + (br ? fb_to_float(br[e]) : 0.0f);
-#pragma unroll
-        for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r)
-            if (e == lane + 32 * r) z[r] = acc;
+    for (int r = 0; r < MOE_MAX_LOGITS_PER_LANE; ++r) {
+        const int e = lane + 32 * r;
+        z[r] = e < E ? logit(e) + (br ? fb_to_float(br[e]) : 0.0f) : -INFINITY;
     }
-    if (w_gate) {
-        float acc = 0.0f;
-        for (int d = lane; d < D; d += 32) acc = fmaf(fb_to_float(x[d]), fb_to_float(w_gate[d]), acc);
-        acc = fb_warp_sum(acc);
-        if (lane == 0) gate[row] = 1.0f / (1.0f + expf(-acc));
-    }
+    if (gate_col >= 0 && lane == 0) gate[row] = 1.0f / (1.0f + expf(-logit(gate_col)));
     float first = 0.0f, total = 0.0f, mine = 0.0f;     // lane k keeps the k-th chosen logit (K <= 32)
     for (int k = 0; k < K; ++k) {
         float best = -INFINITY;
@@ -160,18 +155,22 @@ FB_API int fb_moe_gather_rows(const void* h, long long h_stride, int dtype, cons
     return fb_check_launch("moe_gather_rows");
 }
 
-FB_API int fb_moe_route(const void* h, long long h_stride, int h_dtype, const void* wr, const void* br,
-                        const void* w_gate, int w_dtype, int n, int D, int E, int K, int* chosen, float* share,
-                        float* gate, cudaStream_t stream) {
-    FB_REQUIRE(n >= 0 && D > 0 && E > 0 && K > 0 && K <= E, "router: bad sizes n=%d width=%d experts=%d top=%d", n, D, E, K);
+// z: float32 router logits [n, >= E (+1)] (possibly split-K shares), as a product of the token rows with the stacked
+// router matrix left them; br: the router's bias or nullptr; gate_col: the column that holds w_gate . h (negative: none).
+FB_API int fb_moe_choose(const float* z, long long z_stride, int n_partials, long long partial_stride, const void* br,
+                         int w_dtype, int gate_col, int n, int E, int K, int* chosen, float* share, float* gate,
+                         cudaStream_t stream) {
+    FB_REQUIRE(n >= 0 && E > 0 && K > 0 && K <= E, "router: bad sizes n=%d experts=%d top=%d", n, E, K);
     FB_REQUIRE(E <= 32 * MOE_MAX_LOGITS_PER_LANE, "router: %d experts are more than %d", E, 32 * MOE_MAX_LOGITS_PER_LANE);
     FB_REQUIRE(K <= 32, "router: top = %d is more than 32", K);
-    FB_REQUIRE(!w_gate || gate, "router: a gate weight without a place for the gate");
+    FB_REQUIRE(gate_col < 0 || gate, "router: a gate column without a place for the gate");
+    FB_REQUIRE(z_stride >= E && z_stride > gate_col, "router: logit rows are too short");
     if (n == 0) return 0;
-    FB_DISPATCH_DTYPE(h_dtype, T, FB_DISPATCH_DTYPE(w_dtype, TW,
-        (fb_launch((moe_route_kernel<T, TW>), dim3((n + 3) / 4), dim3(128), 0, stream, (const T*)h, (long)h_stride,
-                   (const TW*)wr, (const TW*)br, (const TW*)w_gate, n, D, E, K, chosen, share, gate))));
-    return fb_check_launch("moe_route");
+    if (n_partials < 1) n_partials = 1;
+    FB_DISPATCH_DTYPE(w_dtype, TW,
+        (fb_launch((moe_choose_kernel<TW>), dim3((n + 3) / 4), dim3(128), 0, stream, z, (long)z_stride, n_partials,
+                   (long)partial_stride, (const TW*)br, gate_col, n, E, K, chosen, share, gate)));
+    return fb_check_launch("moe_choose");
 }
 
 // Row tiles the padded order can take at most: every full tile of pairs, and one ragged tile per expert that has any.

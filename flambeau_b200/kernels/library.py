@@ -55,7 +55,7 @@ _SIGNATURES = {
     "fb_gdr_recurrent": (I, [P, P, P, P, L, P, P, P, I, P, I, I, I, I, STREAM]),
     "fb_gdr_out_norm": (I, [P, P, L, I, L, I, P, I, F, P, I, I, I, I, STREAM]),
     # moe.cu
-    "fb_moe_route": (I, [P, L, I, P, P, P, I, I, I, I, I, P, P, P, STREAM]),
+    "fb_moe_choose": (I, [P, L, I, L, P, I, I, I, I, I, P, P, P, STREAM]),
     "fb_moe_max_tiles": (I, [I, I, I]),
     "fb_moe_gather_rows": (I, [P, L, I, P, P, I, I, STREAM]),
     "fb_moe_sort": (I, [P, I, I, I, I, I, P, P, P, STREAM]),

@@ -886,18 +886,18 @@ def gdr_out_norm(o, proj, gate_off: int, weight, eps: float, out, H: int, dv: in
 # ---------------------------------------------------------------------------
 # routed experts
 # ---------------------------------------------------------------------------
-def moe_route(h, wr, br, w_gate, top: int, chosen, share, gate) -> None:
-    """Per token: the `top` experts with the largest router logits (float32), their softmax weights, and (with
-    w_gate) sigmoid(w_gate . h)."""
-    _cuda(h, wr, br, w_gate, chosen, share, gate)
-    n, D = h.shape
-    E = wr.shape[0]
-    if tuple(chosen.shape) != (n, top) or chosen.dtype != torch.int32 or tuple(share.shape) != (n, top) \
-            or share.dtype != torch.float32 or not wr.is_contiguous() or wr.shape[1] != D:
+def moe_choose(z, bias, gate_col: int, experts: int, top: int, chosen, share, gate, n_partials: int = 1,
+               partial_stride: int = 0) -> None:
+    """Per token: the `top` experts with the largest logits z[:, :experts] + bias (float32; z possibly split-K
+    shares), their softmax weights, and (gate_col >= 0) gate = sigmoid(z[:, gate_col])."""
+    _cuda(z, bias, chosen, share, gate)
+    n = z.shape[0]
+    if z.dtype != torch.float32 or tuple(chosen.shape) != (n, top) or chosen.dtype != torch.int32 \
+            or tuple(share.shape) != (n, top) or share.dtype != torch.float32 or z.shape[1] < experts:
         raise KernelError("router: bad shapes")
-    check(lib().fb_moe_route(h.data_ptr(), _rows(h), dtype_code(h), wr.data_ptr(), _ptr(br), _ptr(w_gate),
-                             dtype_code(wr), n, D, E, int(top), chosen.data_ptr(), share.data_ptr(), _ptr(gate),
-                             _stream()), "moe_route")
+    check(lib().fb_moe_choose(z.data_ptr(), _rows(z), int(n_partials), int(partial_stride), _ptr(bias),
+                              dtype_code(bias) if bias is not None else 0, int(gate_col), n, int(experts), int(top),
+                              chosen.data_ptr(), share.data_ptr(), _ptr(gate), _stream()), "moe_choose")
 
 
 def moe_max_tiles(pairs: int, experts: int, tile: int) -> int:

@@ -42,7 +42,7 @@ SIZES = {
 CLASS_OF = {"paged_attention_mma": "attention", "paged_attention_simt": "attention", "rope_kv_write": "cache_write",
             "qk_norm_rope_kv_write": "cache_write", "add_rms_norm": "norm", "gate_mul": "gate_mul",
             "gdr_prepare": "recurrence_prepare", "gdr_recurrent": "recurrence", "gdr_out_norm": "recurrence_out",
-            "branch_norm_mix": "branch_mix", "moe_route": "router", "moe_sort": "expert_order",
+            "branch_norm_mix": "branch_mix", "moe_choose": "router", "moe_sort": "expert_order",
             "moe_gather_rows": "expert_gather", "moe_combine": "expert_combine", "activation": "activation",
             "gemm_tc_grouped": "routed_product", "gemm_simt_grouped": "routed_product"}
 

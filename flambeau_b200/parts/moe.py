@@ -5,7 +5,7 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward, TensorSpec
-from .linear import Linear
+from .linear import Linear, concat_rows
 from .spec import register_part
 
 
@@ -20,7 +20,8 @@ class RoutedExperts(FeedForward):
     Tensors behind the prefix: e<i>.up [inner, width], e<i>.down [width, inner], router [experts, width], router.b
     [experts], and with a shared expert shared.up, shared.down, shared.sg [1, width].
 
-    How a step runs: the router (one warp a token), a counting sort of the (token, choice) pairs into expert order
+    How a step runs: the router's logits and the shared expert's gate as one product, the choice (one warp a token), a
+    counting sort of the (token, choice) pairs into expert order
     with every expert's stretch padded to whole row tiles, two grouped products over that order (the first gathers
     the tokens' rows and applies the activation), and one kernel that brings the weighted outputs back to the
     tokens and adds the shared expert.  All sizes on the host are upper bounds, so nothing is read back and the
@@ -40,7 +41,7 @@ class RoutedExperts(FeedForward):
         self.shared_inner = int(shared_inner) if shared_inner else 0
         self.router_bias, self.init_std, self.router_std = bool(router_bias), init_std, router_std
         self.up = self.down = self.router = self.router_b = None
-        self.shared_up = self.shared_down = self.shared_gate = None
+        self.shared_up = self.shared_down = None
 
     def own_tensor_specs(self):
         p, init = self.prefix, ("normal", self.init_std)
@@ -61,16 +62,23 @@ class RoutedExperts(FeedForward):
         p = self.prefix
         self.up = torch.stack([tensors[f"{p}e{e}.up"] for e in range(self.E)]).contiguous()        # [E, inner, width]
         self.down = torch.stack([tensors[f"{p}e{e}.down"] for e in range(self.E)]).contiguous()    # [E, width, inner]
-        self.router = tensors[p + "router"].contiguous()
-        self.router_b = tensors[p + "router.b"].to(self.router.dtype).contiguous() if self.router_bias else None
+        # the router and the shared expert's gate are one product: the gate's row lies behind the experts' rows
+        # (then rows of zeros up to a multiple of 8, so that the product's float32 rows stay 16-byte aligned)
+        rows = [tensors[p + "router"]]
+        if self.shared_inner:
+            rows.append(tensors[p + "shared.sg"].reshape(1, self.width).to(rows[0].dtype))
+        have = sum(t.shape[0] for t in rows)
+        if have % 8:
+            rows.append(torch.zeros((8 - have % 8, self.width), dtype=rows[0].dtype, device=rows[0].device))
+        self.router = Linear(concat_rows(rows))
+        self.router_b = tensors[p + "router.b"].to(rows[0].dtype).contiguous() if self.router_bias else None
         if self.shared_inner:
             self.shared_up = Linear(tensors[p + "shared.up"])
             self.shared_down = Linear(tensors[p + "shared.down"])
-            self.shared_gate = tensors[p + "shared.sg"].to(self.router.dtype).reshape(-1).contiguous()
 
     def own_weights(self):
         # a step reads the router, the shared expert, and of the routed experts at most what its tokens choose
-        w = [self.router]
+        w = [self.router.weight]
         if self.shared_inner:
             w += [self.shared_up.weight, self.shared_down.weight]
         return w
@@ -93,7 +101,10 @@ class RoutedExperts(FeedForward):
             chosen = ctx.ws.alloc((n, K), torch.int32)
             share = ctx.ws.alloc((n, K), torch.float32)
             gate = ctx.ws.alloc((n,), torch.float32) if self.shared_inner else None
-            ops.moe_route(h[:n], self.router, self.router_b, self.shared_gate, K, chosen, share, gate)
+            z = ctx.ws.alloc((ctx.max_slabs, n, self.router.out_features), torch.float32)
+            parts = self.router.slabs(ctx, h[:n], z)
+            ops.moe_choose(z[0], self.router_b, E if self.shared_inner else -1, E, K, chosen, share, gate,
+                           n_partials=parts, partial_stride=z.stride(0))
             place_token = ctx.ws.alloc((rows,), torch.int32)
             pair_place = ctx.ws.alloc((pairs,), torch.int32)
             tile_expert = ctx.ws.alloc((max_tiles,), torch.int32)
