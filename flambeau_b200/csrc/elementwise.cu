@@ -898,7 +898,7 @@ struct FbBranches {
 };
 
 template <typename TW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 branch_norm_mix_kernel(FbBranches b, float eps, float weight_offset, float* __restrict__ out, int H) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
@@ -942,7 +942,8 @@ FB_API int fb_branch_norm_mix(int count, const float* const* y, const int* n_par
         b.coef[i] = coef[i];
     }
     FB_DISPATCH_DTYPE(w_dtype, TW,
-        (fb_launch((branch_norm_mix_kernel<TW>), dim3(n), dim3(256), 0, stream, b, eps, weight_offset, out, H)));
+        (fb_launch((branch_norm_mix_kernel<TW>), dim3(n), dim3(n > 128 ? 256 : H >= 2048 ? 1024 : H >= 512 ? 512 : 256), 0, stream, b, eps,
+                   weight_offset, out, H)));
     return fb_check_launch("branch_norm_mix");
 }
 

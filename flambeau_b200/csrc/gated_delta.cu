@@ -12,9 +12,9 @@
 //                    q and k made unit vectors per head (q also times `q_scale`), beta = sigmoid,
 //                    g = exp(-exp(A_log) * softplus(a + dt_bias)); all float32
 //   gdr_conv_tail    per request: the last taps-1 convolution inputs of the step become the kept tail
-//   gdr_recurrent    per (request, head, 16 columns): the recurrence over the step's tokens, state in registers, sixteen
-//                    lanes a column.  Both products with the state are taken from the state before the token's
-//                    update, a = S^T k and b = S^T q, so that they share one exchange between the lanes:
+//   gdr_recurrent    per (request, head, a few columns): the recurrence over the step's tokens, state in registers, 16
+//                    (or 32) lanes a column.  Both products with the state are taken from the state before the
+//                    token's update, a = S^T k and b = S^T q, so that they share one exchange between the lanes:
 //                    u = beta (v - g a), o = g b + u (k . q), S <- g S + k u^T, which is the same arithmetic
 //   gdr_out_norm     per (token, head): o / rms(o) * weight * silu(gate), rounded to the engine's dtype
 //
@@ -112,8 +112,26 @@ __global__ void gdr_conv_tail_kernel(const float* __restrict__ proj, long proj_s
     }
 }
 
-// Sixteen lanes a column, R state values a lane (the key dimension d = lane + 16 r, dk <= 16 R), 16 columns a CTA.
-template <int R>
+// A 4-byte copy from global to shared memory that does not pass through registers (the thread goes on at once).
+__device__ __forceinline__ void gdr_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void gdr_copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int LEFT> __device__ __forceinline__ void gdr_copies_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory");
+}
+
+// LPC lanes a column, R state values a lane (the key dimension d = lane + LPC r, dk <= LPC R), 256 / LPC columns a CTA.
+template <int R, int LPC> struct GdrTile {
+    static constexpr int THREADS = 256, COLS = THREADS / LPC, DKP = LPC * R;
+    // tokens fetched at a time: two such stretches are in shared memory, one being worked on, one arriving
+    static constexpr int CH = DKP <= 128 ? 32 : DKP <= 256 ? 16 : 8;
+    static constexpr int STAGE_FLOATS = CH * (2 * DKP + COLS + 3);
+    __device__ static constexpr int place(int d) { return d; }     // where dimension d of a row lies in shared memory
+};
+
+template <int R, int LPC>
 __global__ void __launch_bounds__(256)
 gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                      float* __restrict__ state, long state_stride, const int* __restrict__ seq_q_start,
@@ -121,14 +139,9 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
                      int G, int H, int dk, int dv) {
     fb_pdl_launch_dependents();
     fb_pdl_wait();
-    constexpr int LPC = 16, COLS = 16, CH = 16, DKP = LPC * R;   // tokens fetched at a time; a key row padded with zeros
-    extern __shared__ float sh[];
-    float* qs = sh;                                    // [CH][DKP]
-    float* ks = qs + CH * DKP;                         // [CH][DKP]
-    float* vs = ks + CH * DKP;                         // [CH][COLS]
-    float* bs = vs + CH * COLS;                        // [CH] beta
-    float* gs = bs + CH;                               // [CH] decay
-    float* kq = gs + CH;                               // [CH] k . q
+    using Tile = GdrTile<R, LPC>;
+    constexpr int THREADS = Tile::THREADS, COLS = Tile::COLS, CH = Tile::CH, DKP = Tile::DKP;
+    extern __shared__ __align__(16) float sh[];
     const int seq = blockIdx.x / H, head = blockIdx.x - seq * H;
     const int g = head / (H / G);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -137,31 +150,61 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
     const int qk = G * dk, C = 2 * qk + H * dv;
     const int start = seq_q_start[seq], L = seq_q_len[seq];
     float* S = state + (size_t)seq_slot[seq] * state_stride + ((size_t)head * dv + (live ? col : 0)) * dk;
+
+    // a stage: q [CH][DKP], k [CH][DKP] (rows padded with zeros beyond dk), v [CH][COLS], beta, decay, k . q [CH] each
+    auto fetch = [&](int t0, float* st) {
+        const int cnt = min(CH, L - t0);
+        float* qs = st;
+        float* ks = qs + CH * DKP;
+        float* vs = ks + CH * DKP;
+        float* bs = vs + CH * COLS;
+        float* gs = bs + CH;
+        for (int e = tid; e < cnt * DKP; e += THREADS) {
+            const int t = e / DKP, d = e - t * DKP;
+            const float* rowp = qkv + (size_t)(start + t0 + t) * C + (size_t)g * dk;
+            const int at = t * DKP + Tile::place(d);
+            if (d < dk) {
+                gdr_copy4(qs + at, rowp + d);
+                gdr_copy4(ks + at, rowp + qk + d);
+            } else {
+                qs[at] = 0.0f;
+                ks[at] = 0.0f;
+            }
+        }
+        for (int e = tid; e < cnt * COLS; e += THREADS) {
+            const int t = e / COLS, c2 = blockIdx.y * COLS + (e - t * COLS);
+            if (c2 < dv) gdr_copy4(vs + e, qkv + (size_t)(start + t0 + t) * C + 2 * qk + (size_t)head * dv + c2);
+            else vs[e] = 0.0f;
+        }
+        if (tid < cnt) {
+            gdr_copy4(bs + tid, beta + (size_t)(start + t0 + tid) * H + head);
+            gdr_copy4(gs + tid, decay + (size_t)(start + t0 + tid) * H + head);
+        }
+        gdr_copies_commit();
+    };
+
     float s[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = li + LPC * r;
         s[r] = (live && d < dk) ? S[d] : 0.0f;
     }
-    for (int t0 = 0; t0 < L; t0 += CH) {
+    if (L > 0) fetch(0, sh);
+    int buf = 0;
+    for (int t0 = 0; t0 < L; t0 += CH, buf ^= 1) {
         const int cnt = min(CH, L - t0);
+        float* st = sh + buf * Tile::STAGE_FLOATS;
+        const bool more = t0 + CH < L;
+        if (more) fetch(t0 + CH, sh + (buf ^ 1) * Tile::STAGE_FLOATS);    // (its last readers passed the barrier below)
+        if (more) gdr_copies_wait<1>(); else gdr_copies_wait<0>();
         __syncthreads();
-        for (int e = tid; e < cnt * DKP; e += 256) {
-            const int t = e / DKP, d = e - t * DKP;
-            const float* rowp = qkv + (size_t)(start + t0 + t) * C + (size_t)g * dk;
-            qs[e] = d < dk ? rowp[d] : 0.0f;
-            ks[e] = d < dk ? rowp[qk + d] : 0.0f;
-        }
-        for (int e = tid; e < cnt * COLS; e += 256) {
-            const int t = e / COLS, c2 = blockIdx.y * COLS + (e - t * COLS);
-            vs[e] = c2 < dv ? qkv[(size_t)(start + t0 + t) * C + 2 * qk + (size_t)head * dv + c2] : 0.0f;
-        }
-        if (tid < cnt) {
-            bs[tid] = beta[(size_t)(start + t0 + tid) * H + head];
-            gs[tid] = decay[(size_t)(start + t0 + tid) * H + head];
-        }
-        __syncthreads();
-        for (int t = warp; t < cnt; t += 8) {
+        const float* qs = st;
+        const float* ks = qs + CH * DKP;
+        const float* vs = ks + CH * DKP;
+        const float* bs = vs + CH * COLS;
+        const float* gs = bs + CH;
+        float* kq = st + CH * (2 * DKP + COLS + 2);
+        for (int t = warp; t < cnt; t += THREADS / 32) {
             float acc = 0.0f;
             for (int d = lane; d < DKP; d += 32) acc = fmaf(ks[t * DKP + d], qs[t * DKP + d], acc);
             acc = fb_warp_sum(acc);
@@ -169,7 +212,7 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
         }
         __syncthreads();
         for (int t = 0; t < cnt; ++t) {
-            const float gt = gs[t], bt = bs[t];
+            const float gt = gs[t];
             const float* kt = ks + t * DKP + li;
             const float* qt = qs + t * DKP + li;
             float kk[R];
@@ -187,12 +230,13 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
                 a += __shfl_xor_sync(0xffffffffu, a, off);
                 b += __shfl_xor_sync(0xffffffffu, b, off);
             }
-            const float u = bt * (vs[t * COLS + tid / LPC] - gt * a);
+            const float u = bs[t] * (vs[t * COLS + tid / LPC] - gt * a);
 #pragma unroll
             for (int r = 0; r < R; ++r) s[r] = fmaf(kk[r], u, gt * s[r]);
             if (live && li == 0)
                 o[(size_t)(start + t0 + t) * H * dv + (size_t)head * dv + col] = fmaf(u, kq[t], gt * b);
         }
+        __syncthreads();                               // the stage may be overwritten by the fetch after next
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -252,16 +296,16 @@ FB_API int fb_gdr_prepare(const float* proj, long long proj_stride, int n_partia
     return fb_check_launch("gdr_conv_tail");
 }
 
-template <int R>
+template <int R, int LPC>
 static int launch_gdr_recurrent(const float* qkv, const float* beta, const float* decay, float* state,
                                 long state_stride, const int* seq_q_start, const int* seq_q_len, const int* seq_slot,
                                 int n_seqs, float* o, int G, int H, int dk, int dv, cudaStream_t stream) {
-    constexpr int COLS = 16, CH = 16, DKP = 16 * R;
-    const size_t smem = ((size_t)2 * CH * DKP + CH * COLS + 3 * CH) * sizeof(float);
-    auto kernel = gdr_recurrent_kernel<R>;
+    using Tile = GdrTile<R, LPC>;
+    const size_t smem = (size_t)2 * Tile::STAGE_FLOATS * sizeof(float);
+    auto kernel = gdr_recurrent_kernel<R, LPC>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    fb_launch(kernel, dim3(n_seqs * H, (dv + COLS - 1) / COLS), dim3(256), smem, stream, qkv, beta, decay, state,
-              state_stride, seq_q_start, seq_q_len, seq_slot, o, G, H, dk, dv);
+    fb_launch(kernel, dim3(n_seqs * H, (dv + Tile::COLS - 1) / Tile::COLS), dim3(Tile::THREADS), smem, stream, qkv, beta,
+              decay, state, state_stride, seq_q_start, seq_q_len, seq_slot, o, G, H, dk, dv);
     return fb_check_launch("gdr_recurrent");
 }
 
@@ -271,15 +315,17 @@ FB_API int fb_gdr_recurrent(const float* qkv, const float* beta, const float* de
     FB_REQUIRE(n_seqs >= 0 && G > 0 && H > 0 && H % G == 0 && dk > 0 && dv > 0, "gated delta: bad sizes");
     FB_REQUIRE(dk <= 1024, "gated delta: key size %d is larger than 1024", dk);
     if (n_seqs == 0) return 0;
-#define FB_GDR_CASE(R) return launch_gdr_recurrent<R>(qkv, beta, decay, state, (long)state_stride, seq_q_start, \
+#define FB_GDR_CASE(R, LPC) return launch_gdr_recurrent<R, LPC>(qkv, beta, decay, state, (long)state_stride, seq_q_start, \
         seq_q_len, seq_slot, n_seqs, o, G, H, dk, dv, stream)
-    if (dk <= 16) FB_GDR_CASE(1);
-    if (dk <= 32) FB_GDR_CASE(2);
-    if (dk <= 64) FB_GDR_CASE(4);
-    if (dk <= 128) FB_GDR_CASE(8);
-    if (dk <= 256) FB_GDR_CASE(16);
-    if (dk <= 512) FB_GDR_CASE(32);
-    FB_GDR_CASE(64);
+    // (sixteen lanes a column and 256 threads measured fastest for keys of 128: fewer lanes leave too few warps to
+    // hide the exchange between lanes, more lanes spend their instructions on that exchange)
+    if (dk <= 16) FB_GDR_CASE(1, 16);
+    if (dk <= 32) FB_GDR_CASE(2, 16);
+    if (dk <= 64) FB_GDR_CASE(4, 16);
+    if (dk <= 128) FB_GDR_CASE(8, 16);
+    if (dk <= 256) FB_GDR_CASE(16, 16);
+    if (dk <= 512) FB_GDR_CASE(16, 32);
+    FB_GDR_CASE(32, 32);
 #undef FB_GDR_CASE
 }
 

@@ -18,7 +18,7 @@ __device__ __forceinline__ float qkr_slab_sum(const float* row, int c, int n_par
 }
 
 template <typename TW, typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 qk_norm_rope_kv_write_kernel(const float* __restrict__ proj, long proj_stride, int n_partials, long partial_stride,
                              const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, int scope, float eps,
                              float weight_offset, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -135,7 +135,8 @@ FB_API int fb_qk_norm_rope_kv_write(const float* proj, long long proj_stride, in
     FB_DISPATCH_DTYPE(w_dtype, TW, FB_DISPATCH_DTYPE(out_dtype, T, {
         auto kernel = qk_norm_rope_kv_write_kernel<TW, T>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        fb_launch(kernel, dim3(n), dim3(256), smem, stream, proj, (long)proj_stride, n_partials, (long)partial_stride,
+        const int cols = (nh + 2 * nkv) * (hd > vd ? hd : vd);
+        fb_launch(kernel, dim3(n), dim3(n > 128 ? 256 : cols >= 4096 ? 1024 : cols >= 1024 ? 512 : 256), smem, stream, proj, (long)proj_stride, n_partials, (long)partial_stride,
                   (const TW*)q_weight, (const TW*)k_weight, scope, eps, weight_offset, cos_t, sin_t, half, (T*)q_out,
                   (long)q_out_stride, positions, row_seq, block_table, table_stride, table_base, (T*)k_pool,
                   (T*)v_pool, page_size, n_pages, nh, nkv, hd, vd, write_kv, status);

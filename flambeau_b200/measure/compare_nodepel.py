@@ -100,6 +100,16 @@ def measure(name: str, size: dict, layers: int, batch: int, context: int, prefil
                "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prefill / (pre_ms / 1e3), 1),
                "weight_bytes": engine.model.step_weight_bytes(), "kv_bytes_per_token": engine.cache.kv_bytes_per_token(),
                "state_bytes_per_request": engine.cache.state_bytes_per_request()}
+        # what a decode step must read: every weight that takes part (of the routed experts those that the batch's
+        # tokens are expected to choose between them, each once), the live keys and values, and the state twice
+        nbytes = work.decode_step_bytes(rec["weight_bytes"], rec["kv_bytes_per_token"], [context] * batch, size["window"])
+        if design == "nodepel":
+            E, K = size["experts"], size["top"]
+            distinct = E * (1.0 - (1.0 - K / E) ** batch)
+            per_expert = 2 * size["width"] * size["expert_ff"] * 2
+            nbytes += layers * (distinct - K) * per_expert + 2 * batch * rec["state_bytes_per_request"]
+        rec["decode_bytes"] = int(nbytes)
+        rec["decode_hbm_frac"] = round(nbytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
         vocab = engine.model.vocab_size
         ids = workloads.seat(engine, [context] * batch)
         entries = [Entry(r, [int(torch.randint(0, vocab, (1,), generator=gen))], [0]) for r in ids]
