@@ -421,6 +421,53 @@ def test_no_loop_at_all(tmp_path):
     run(c, tiny.schedule_portions(requests, sizes=(5, 2, 9)), tmp_path / "o")
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: widths that are and are not multiples of 8, odd head sizes, windows from one
+    key to beyond the requests, rotations of none, part or all of a head, one to five taps, one to a dozen experts
+    with and without a shared one, layers without feed-forward, a loop anywhere or none."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([40, 72, 100, 128, 36])
+    n_layers = rng.randint(1, 4)
+    layers = []
+    for _ in range(n_layers):
+        g = rng.choice([1, 2, 3])
+        h = g * rng.choice([1, 2, 4])
+        d = rng.choice([8, 12, 16, 20, 24, 32, 40, 64])
+        e = rng.choice([d, d, 8, 24, 48])
+        dims = rng.choice([0, 2, d // 2 // 2 * 2, d // 2 * 2])
+        Gr = rng.choice([1, 2, 3])
+        Hr = Gr * rng.choice([1, 2])
+        mlp = None
+        if rng.random() < 0.8:
+            experts = rng.randint(1, 12)
+            mlp = (experts, rng.randint(1, min(experts, 4)), rng.choice([8, 16, 24, 40]), rng.choice([None, 8, 32]))
+        layers.append(nt.layer((h, g, d, e, rng.choice([1, 2, 5, 16, 17, 31, 64, 500]), rng.choice([100.0, 1e4, 1e6]), dims,
+                                rng.uniform(0.1, 0.4)),
+                               (Hr, Gr, rng.choice([4, 8, 12, 16, 36, 72]), rng.choice([8, 12, 16, 40]), rng.randint(1, 5)),
+                               mlp))
+    cfg = {"architecture": "Nodepel", "embedding": {"scale": rng.uniform(0.3, 3.0)}, "norm": {"eps": rng.choice([1e-5, 1e-6])},
+           "vocab": rng.randint(50, 400), "width": width, "layers": layers}
+    if rng.random() < 0.7:
+        start = rng.randint(0, n_layers - 1)
+        cfg["loop"] = {"start": start, "stop": rng.randint(start + 1, n_layers), "times": rng.randint(1, 3)}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", [101, 102, 103, 104, 105, 106, 107, 108])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_configurations_under_a_mixed_schedule(tmp_path, seed, dtype):
+    cfg = random_config(seed)
+    folder = nt.make_folder(tmp_path / "m", cfg, seed=seed, dtype=dtype, sharp=SHARP[dtype],
+                            steady_router=dtype == "bfloat16")
+    requests = tiny.random_requests({"vocab_size": cfg["vocab"]}, [1, 37, 80, 2, 55, 21], seed=seed)
+    pcfg, W = pn.load_folder(folder)
+    c = dict(name=f"random {seed}", dtype=dtype, cfg=cfg, folder=folder, requests=requests,
+             want={rid: pn.forward(pcfg, W, toks) for rid, toks in requests.items()},
+             tol=tolerance(dtype, pcfg, W, requests))
+    run(c, tiny.schedule_mixed(requests, seed=seed), tmp_path / "o")
+
+
 def test_the_state_carries_a_far_token_and_the_window_does_not(tmp_path):
     """One layer, float32.  With the recurrent side's output weight zeroed only the window is left: changing the token
     just outside the last query's window leaves its logits as they were, changing the one just inside moves them.
