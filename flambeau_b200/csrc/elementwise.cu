@@ -848,12 +848,34 @@ __global__ void activation_kernel(const TI* __restrict__ z, long stride, int n_p
     out[idx] = fb_from_float<T>(fb_plain_act(act, slab_sum(z + (size_t)r * stride, c, n_partials, partial_stride)));
 }
 
+// Four outputs per thread from 4-wide loads; I and the strides multiples of 4, aligned rows.
+template <typename TI, typename T>
+__global__ void activation_vec_kernel(const TI* __restrict__ z, long stride, int n_partials, long partial_stride,
+                                      T* __restrict__ out, int n, int I, int act) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int nvec = I >> 2;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * nvec) return;
+    const int r = (int)(idx / nvec), c = (int)(idx - (size_t)r * nvec);
+    float4 v = slab_sum4(z + (size_t)r * stride + 4 * c, n_partials, partial_stride);
+    v.x = fb_plain_act(act, v.x); v.y = fb_plain_act(act, v.y); v.z = fb_plain_act(act, v.z); v.w = fb_plain_act(act, v.w);
+    Vec4<T>::store(out + (size_t)r * I + 4 * c, v);
+}
+
 FB_API int fb_activation(const void* z, long long stride, int in_dtype, int n_partials, long long partial_stride,
                          void* out, int out_dtype, int n, int I, int act, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && I > 0 && stride >= I, "activation: bad sizes n=%d I=%d stride=%lld", n, I, stride);
     FB_REQUIRE(fb_plain_act_known(act), "activation: unknown activation code %d", act);
     if (n == 0) return 0;
     if (n_partials < 1) n_partials = 1;
+    if (I % 4 == 0 && stride % 4 == 0 && partial_stride % 4 == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const size_t total4 = (size_t)n * (I / 4);
+        FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
+            (fb_launch((activation_vec_kernel<TI, T>), (unsigned)((total4 + 255) / 256), 256, 0, stream,
+                (const TI*)z, (long)stride, n_partials, (long)partial_stride, (T*)out, n, I, act))));
+        return fb_check_launch("activation");
+    }
     const size_t total = (size_t)n * I;
     FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, T,
         (fb_launch((activation_kernel<TI, T>), (unsigned)((total + 255) / 256), 256, 0, stream,

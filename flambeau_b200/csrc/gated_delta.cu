@@ -15,7 +15,8 @@
 //   gdr_recurrent    per (request, head, a few columns): the recurrence over the step's tokens, state in registers, 16
 //                    (or 32) lanes a column.  Both products with the state are taken from the state before the
 //                    token's update, a = S^T k and b = S^T q, so that they share one exchange between the lanes:
-//                    u = beta (v - g a), o = g b + u (k . q), S <- g S + k u^T, which is the same arithmetic
+//                    u = beta (v - g a), o = g b + u (k . q), S <- g S + k u^T, which is the same arithmetic; and two
+//                    tokens are taken at a time, the second one's products following from the first one's correction
 //   gdr_out_norm     per (token, head): o / rms(o) * weight * silu(gate), rounded to the engine's dtype
 //
 // A request's slot of state is one float32 array: S as [heads][dv][dk] (a column's dk values side by side), then the
@@ -127,7 +128,7 @@ template <int R, int LPC> struct GdrTile {
     static constexpr int THREADS = 256, COLS = THREADS / LPC, DKP = LPC * R;
     // tokens fetched at a time: two such stretches are in shared memory, one being worked on, one arriving
     static constexpr int CH = DKP <= 128 ? 32 : DKP <= 256 ? 16 : 8;
-    static constexpr int STAGE_FLOATS = CH * (2 * DKP + COLS + 3);
+    static constexpr int STAGE_FLOATS = CH * (2 * DKP + COLS + 5);
     __device__ static constexpr int place(int d) { return d; }     // where dimension d of a row lies in shared memory
 };
 
@@ -151,7 +152,8 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
     const int start = seq_q_start[seq], L = seq_q_len[seq];
     float* S = state + (size_t)seq_slot[seq] * state_stride + ((size_t)head * dv + (live ? col : 0)) * dk;
 
-    // a stage: q [CH][DKP], k [CH][DKP] (rows padded with zeros beyond dk), v [CH][COLS], beta, decay, k . q [CH] each
+    // a stage: q [CH][DKP], k [CH][DKP] (rows padded with zeros beyond dk), v [CH][COLS], then [CH] each: beta, decay,
+    // k_t . q_t, k_t . k_t+1, k_t . q_t+1
     auto fetch = [&](int t0, float* st) {
         const int cnt = min(CH, L - t0);
         float* qs = st;
@@ -204,14 +206,66 @@ gdr_recurrent_kernel(const float* __restrict__ qkv, const float* __restrict__ be
         const float* bs = vs + CH * COLS;
         const float* gs = bs + CH;
         float* kq = st + CH * (2 * DKP + COLS + 2);
+        float* kkn = kq + CH;                          // k_t . k_t+1
+        float* kqn = kkn + CH;                         // k_t . q_t+1
         for (int t = warp; t < cnt; t += THREADS / 32) {
-            float acc = 0.0f;
-            for (int d = lane; d < DKP; d += 32) acc = fmaf(ks[t * DKP + d], qs[t * DKP + d], acc);
+            const bool pair = !(t & 1) && t + 1 < cnt;
+            float acc = 0.0f, acc_k = 0.0f, acc_q = 0.0f;
+            for (int d = lane; d < DKP; d += 32) {
+                const float kd = ks[t * DKP + d];
+                acc = fmaf(kd, qs[t * DKP + d], acc);
+                if (pair) {
+                    acc_k = fmaf(kd, ks[(t + 1) * DKP + d], acc_k);
+                    acc_q = fmaf(kd, qs[(t + 1) * DKP + d], acc_q);
+                }
+            }
             acc = fb_warp_sum(acc);
-            if (lane == 0) kq[t] = acc;
+            acc_k = fb_warp_sum(acc_k);
+            acc_q = fb_warp_sum(acc_q);
+            if (lane == 0) { kq[t] = acc; kkn[t] = acc_k; kqn[t] = acc_q; }
         }
         __syncthreads();
-        for (int t = 0; t < cnt; ++t) {
+        int t = 0;
+        // Two tokens at a time: all four products with the state are taken from the state before either update and
+        // share one exchange between the lanes; the second token's follow from the first's correction:
+        //   S_t^T k_t+1 = g_t S_t-1^T k_t+1 + u_t (k_t . k_t+1), and likewise for q_t+1;
+        //   S_t+1 = g_t+1 g_t S_t-1 + g_t+1 k_t u_t^T + k_t+1 u_t+1^T.
+        for (; t + 1 < cnt; t += 2) {
+            const float g0 = gs[t], g1 = gs[t + 1];
+            const float* k0p = ks + t * DKP + li;
+            const float* q0p = qs + t * DKP + li;
+            float k0[R], k1[R];
+            float a0 = 0.0f, b0 = 0.0f, a1 = 0.0f, b1 = 0.0f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                k0[r] = k0p[LPC * r];
+                k1[r] = k0p[DKP + LPC * r];
+                a0 = fmaf(s[r], k0[r], a0);
+                b0 = fmaf(s[r], q0p[LPC * r], b0);
+                a1 = fmaf(s[r], k1[r], a1);
+                b1 = fmaf(s[r], q0p[DKP + LPC * r], b1);
+            }
+#pragma unroll
+            for (int off = LPC / 2; off > 0; off >>= 1) {
+                a0 += __shfl_xor_sync(0xffffffffu, a0, off);
+                b0 += __shfl_xor_sync(0xffffffffu, b0, off);
+                a1 += __shfl_xor_sync(0xffffffffu, a1, off);
+                b1 += __shfl_xor_sync(0xffffffffu, b1, off);
+            }
+            const float u0 = bs[t] * (vs[t * COLS + tid / LPC] - g0 * a0);
+            const float a1n = fmaf(u0, kkn[t], g0 * a1);
+            const float u1 = bs[t + 1] * (vs[(t + 1) * COLS + tid / LPC] - g1 * a1n);
+            const float b1n = fmaf(u0, kqn[t], g0 * b1);
+            const float gg = g1 * g0, gu = g1 * u0;
+#pragma unroll
+            for (int r = 0; r < R; ++r) s[r] = fmaf(k1[r], u1, fmaf(k0[r], gu, gg * s[r]));
+            if (live && li == 0) {
+                float* op = o + (size_t)(start + t0 + t) * H * dv + (size_t)head * dv + col;
+                op[0] = fmaf(u0, kq[t], g0 * b0);
+                op[(size_t)H * dv] = fmaf(u1, kq[t + 1], g1 * b1n);
+            }
+        }
+        for (; t < cnt; ++t) {
             const float gt = gs[t];
             const float* kt = ks + t * DKP + li;
             const float* qt = qs + t * DKP + li;

@@ -71,7 +71,7 @@ __device__ __forceinline__ Unit unit_of(int u, int tiles_m, int tiles_n, int spl
 
 // Persistent: the grid is at most one or two CTAs per SM; CTA c takes units c, c + grid, c + 2*grid, ...
 // The TMA pipeline runs on across units, and the accumulator alternates between two regions of tensor memory.
-template <int BN, typename TO>
+template <int BN, typename TO, bool ACT>     // ACT: the epilogue applies the plain activation `plain_act`
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TO* __restrict__ out, long ldo, long slab_stride, float* __restrict__ partials,
@@ -270,7 +270,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                             for (int q = 0; q < 16; ++q)
                                 if (m0 + c + q < M)
-                                    dst[(size_t)(m0 + c + q) * ldo + n] = fb_from_float<TO>(fb_plain_act(plain_act, v[q]));
+                                    dst[(size_t)(m0 + c + q) * ldo + n] =
+                                        fb_from_float<TO>(ACT ? fb_plain_act(plain_act, v[q]) : v[q]);
                         }
                     }
                 }
@@ -351,7 +352,7 @@ int pick_splits(int tiles, int kb_total, int slots, int max_splits, double share
     return best;
 }
 
-template <int BN, typename TO>
+template <int BN, typename TO, bool ACT = false>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo, long slab_stride, int max_slabs,
               int* splits_used, float* partials, long partial_floats, int* counters, int n_counters, int M, int N,
               int K, int force_splits, int* status, cudaStream_t stream, int gated = 0,
@@ -379,7 +380,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, long ldo,
     if (splits_used) *splits_used = splits;
     const long n_units = (long)tiles * splits;
     if (n_units > 2000000000L) return fb_fail(-1, "gemm_tc: too many tiles (M=%d N=%d)", M, N);
-    auto kern = gemm_tc_kernel<BN, TO>;
+    auto kern = gemm_tc_kernel<BN, TO, ACT>;
     static bool configured[FB_MAX_DEVICES] = {};
     if (fb_needs_setup(configured)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -473,11 +474,16 @@ FB_API int fb_gemm_tc_grouped(const void* X, long long lda, const void* W, long 
 #define FB_TCGR_CASE(BN_)                                                                                       \
     case BN_:                                                                                                   \
         if (o_dtype == FB_F32)                                                                                  \
-            return launch_tc<BN_, float>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, M, N, K, \
-                                         1, status, stream, 0, tile_group, N, act);                             \
+            return act ? launch_tc<BN_, float, true>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, M, \
+                                                     N, K, 1, status, stream, 0, tile_group, N, act)            \
+                       : launch_tc<BN_, float>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, M, N, K, \
+                                               1, status, stream, 0, tile_group, N, 0);                         \
         else if (o_dtype == FB_BF16)                                                                            \
-            return launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, \
-                                                 M, N, K, 1, status, stream, 0, tile_group, N, act);            \
+            return act ? launch_tc<BN_, __nv_bfloat16, true>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, \
+                                                             nullptr, 0, M, N, K, 1, status, stream, 0,         \
+                                                             tile_group, N, act)                                \
+                       : launch_tc<BN_, __nv_bfloat16>(mw, mx, out, (long)ldo, 0, 1, nullptr, nullptr, 0, nullptr, 0, \
+                                                       M, N, K, 1, status, stream, 0, tile_group, N, 0);        \
         break;
     switch (tile) {
         FB_TCGR_CASE(16)

@@ -188,11 +188,53 @@ FB_API int fb_moe_sort(const int* chosen, int pairs, int K, int E, int tile, int
     return fb_check_launch("moe_sort");
 }
 
+// Four columns a thread (D a multiple of 4, rows 16-byte aligned): a token's places and shares are fetched once per
+// four outputs and every row is read 16 bytes at a time.
+__global__ void moe_combine_vec_kernel(const float* __restrict__ expert_out, long expert_stride,
+                                       const int* __restrict__ pair_place, const float* __restrict__ share, int K,
+                                       const float* __restrict__ shared_out, int shared_partials,
+                                       long shared_partial_stride, const float* __restrict__ gate,
+                                       float* __restrict__ out, int n, int D) {
+    fb_pdl_launch_dependents();
+    fb_pdl_wait();
+    const int nvec = D >> 2;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n * nvec) return;
+    const int row = (int)(idx / nvec), c = (int)(idx - (size_t)row * nvec) * 4;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int k = 0; k < K; ++k) {
+        const int at = pair_place[(size_t)row * K + k];
+        if (at < 0) continue;
+        const float w = share[(size_t)row * K + k];
+        const float4 v = *reinterpret_cast<const float4*>(expert_out + (size_t)at * expert_stride + c);
+        acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+    }
+    if (shared_out) {
+        float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int p = 0; p < shared_partials; ++p) {
+            const float4 v = *reinterpret_cast<const float4*>(shared_out + (size_t)p * shared_partial_stride +
+                                                              (size_t)row * D + c);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        const float gt = gate ? gate[row] : 1.0f;
+        acc.x = fmaf(gt, s.x, acc.x); acc.y = fmaf(gt, s.y, acc.y); acc.z = fmaf(gt, s.z, acc.z); acc.w = fmaf(gt, s.w, acc.w);
+    }
+    *reinterpret_cast<float4*>(out + (size_t)row * D + c) = acc;
+}
+
 FB_API int fb_moe_combine(const float* expert_out, long long expert_stride, const int* pair_place, const float* share,
                           int K, const float* shared_out, int shared_partials, long long shared_partial_stride,
                           const float* gate, float* out, int n, int D, cudaStream_t stream) {
     FB_REQUIRE(n >= 0 && D > 0 && K > 0, "moe_combine: bad sizes");
     if (n == 0) return 0;
+    if (D % 4 == 0 && expert_stride % 4 == 0 && shared_partial_stride % 4 == 0 && (uintptr_t)expert_out % 16 == 0 &&
+        (uintptr_t)out % 16 == 0 && (!shared_out || (uintptr_t)shared_out % 16 == 0)) {
+        const size_t total4 = (size_t)n * (D / 4);
+        fb_launch(moe_combine_vec_kernel, dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, stream, expert_out,
+                  (long)expert_stride, pair_place, share, K, shared_out, shared_partials < 1 ? 1 : shared_partials,
+                  (long)shared_partial_stride, gate, out, n, D);
+        return fb_check_launch("moe_combine");
+    }
     const size_t total = (size_t)n * D;
     fb_launch(moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, expert_out,
               (long)expert_stride, pair_place, share, K, shared_out, shared_partials < 1 ? 1 : shared_partials,
