@@ -102,6 +102,19 @@ def test_random_folder_is_read_back_by_the_oracle(tmp_path):
     assert logits.shape == (7, 96) and bool(torch.isfinite(logits).all())
 
 
+def test_command_line_writes_and_inspects_a_model(tmp_path, capsys):
+    import json
+    from flambeau_b200.cli import main
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(nt.CONFIG_NC))
+    assert main(["random-model", "--config", str(cfg_file), "--out", str(tmp_path / "m"), "--seed", "3"]) == 0
+    assert main(["inspect", "--model", str(tmp_path / "m")]) == 0
+    out = capsys.readouterr().out
+    assert '"architecture": "Nodepel"' in out and "l1.mix.right.A_log" in out and "l0.mlp.e4.down" in out
+    cfg, w = pn.load_folder(tmp_path / "m")
+    assert pn.forward(cfg, w, [1, 2, 3]).shape == (3, nt.CONFIG_NC["vocab"])
+
+
 def test_plain_mechanisms():
     g = torch.Generator().manual_seed(0)
     # the window: itself and size - 1 tokens before it

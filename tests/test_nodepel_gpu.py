@@ -535,3 +535,43 @@ def test_greedy_generation(tmp_path, name, dtype):
                 gap = float(best - logits[t]) / float(logits.abs().max())
                 assert gap <= 2 * tol, f"token {t} is {gap:.3f} of the scale below the best logit"
             toks.append(t)
+
+
+def test_command_line_infer_and_replay(tmp_path):
+    """The programs a user runs: `flambeau infer` (greedy, float32: the tokens are the plain implementation's) and
+    `bin/trace_run` fed two requests step by step (their last logits are the plain implementation's)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    import numpy as np
+    root = Path(__file__).resolve().parent.parent
+    cfg = nt.CONFIGS["NC"]
+    folder = nt.make_folder(tmp_path / "m", cfg, seed=12, dtype="float32")
+    pcfg, W = pn.load_folder(folder)
+    prompt = tiny.random_requests({"vocab_size": cfg["vocab"]}, [14], seed=3)["r0"]
+    proc = subprocess.run([sys.executable, str(root / "bin" / "flambeau"), "infer", "--model", str(folder), "--max-tokens",
+                           "4", "--dtype", "float32", "--prompt", ",".join(map(str, prompt))],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    out = [int(t) for t in proc.stdout.strip().splitlines()[-1].split(",")]
+    toks = list(prompt)
+    for t in out:
+        logits = pn.forward(pcfg, W, toks)[-1]
+        assert t == int((logits == logits.max()).nonzero()[0])
+        toks.append(t)
+    other = tiny.random_requests({"vocab_size": cfg["vocab"]}, [9], seed=5)["r0"]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": prompt[:6], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": prompt[6:13], "want": []},
+                                     {"id": "b", "tokens": other[:8], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "b", "tokens": other[8:], "want": [0]},
+                                     {"id": "a", "tokens": prompt[13:], "want": [0]}], "end": ["a", "b"]}]
+    proc = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out",
+                           str(tmp_path / "o"), "--max-tokens", "128"], input="\n".join(json.dumps(x) for x in steps) + "\n",
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    got = np.fromfile(tmp_path / "o" / "2.f32", dtype="<f4").reshape(2, cfg["vocab"])
+    for row, seq in zip(got, (other, prompt)):
+        want = pn.forward(pcfg, W, seq)[-1]
+        assert rel_err(torch.from_numpy(row.copy()), want) < 1e-4
