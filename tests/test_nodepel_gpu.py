@@ -268,11 +268,14 @@ def test_gated_delta_rule_across_steps(sizes):
 
 
 @pytest.mark.parametrize("shape", [(5, 64, 6, 2, 24, 40), (300, 96, 40, 5, 16, 24), (33, 32, 4, 1, 32, 0),
-                                   (2, 48, 3, 3, 20, 8), (700, 64, 8, 2, 40, 0)], ids=str)
+                                   (2, 48, 3, 3, 20, 8), (700, 64, 8, 2, 40, 0), (900, 64, 4, 2, 40, 16),
+                                   (1300, 128, 5, 3, 136, 0)], ids=str)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_routed_experts(shape, dtype, tmp_path):
     """The part alone: router, choice, shares, the grouped products and the shared expert against the plain
-    implementation; the router's weights are wide, so that choices are rarely close."""
+    implementation; the router's weights are wide, so that choices are rarely close.  The shapes reach every row tile
+    of the grouped products (16 rows while experts hold few tokens, 64, and 128 on the tensor cores once they hold
+    hundreds)."""
     from flambeau_b200.engine.runtime import Runtime
     from flambeau_b200.parts.moe import RoutedExperts
     n, D, E, K, ff, shared = shape
@@ -466,6 +469,24 @@ def test_random_configurations_under_a_mixed_schedule(tmp_path, seed, dtype):
              want={rid: pn.forward(pcfg, W, toks) for rid, toks in requests.items()},
              tol=tolerance(dtype, pcfg, W, requests))
     run(c, tiny.schedule_mixed(requests, seed=seed), tmp_path / "o")
+
+
+def test_heads_of_64_and_128_in_bfloat16(tmp_path):
+    """Head sizes that the tensor-core attention for portions takes (64 and 128, values as wide as keys), prompts of a
+    few hundred tokens fed whole, in portions and token by token, so that the sink passes every one of its kernels
+    inside a whole model."""
+    cfg = {"architecture": "Nodepel", "embedding": {"scale": 1.5}, "norm": {"eps": 1e-6}, "vocab": 300, "width": 128,
+           "layers": [nt.layer((4, 2, 64, 64, 70, 1e4, 32, 0.125), (2, 1, 32, 64, 4), (6, 2, 32, 64)),
+                      nt.layer((2, 1, 128, 128, 150, 1e6, 128, 0.09), (4, 2, 64, 32, 2), None)]}
+    folder = nt.make_folder(tmp_path / "m", cfg, seed=23, dtype="bfloat16", sharp=SHARP["bfloat16"], steady_router=True)
+    requests = tiny.random_requests({"vocab_size": cfg["vocab"]}, [330, 40, 170], seed=9)
+    pcfg, W = pn.load_folder(folder)
+    c = dict(name="wide heads", dtype="bfloat16", cfg=cfg, folder=folder, requests=requests,
+             want={rid: pn.forward(pcfg, W, toks) for rid, toks in requests.items()},
+             tol=tolerance("bfloat16", pcfg, W, requests))
+    run(c, tiny.schedule_whole(requests), tmp_path / "w")
+    run(c, tiny.schedule_portions(requests, sizes=(150, 2, 64, 33, 17)), tmp_path / "p")
+    run(c, tiny.schedule_tail(requests, 20), tmp_path / "t")
 
 
 def test_the_state_carries_a_far_token_and_the_window_does_not(tmp_path):
