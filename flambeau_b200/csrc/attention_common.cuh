@@ -29,6 +29,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+// What rounding to bfloat16 left of two numbers, as a bfloat16 pair again.
+__device__ __forceinline__ uint32_t pack_bf16_remainder(float lo, float hi) {
+    return pack_bf16(lo - __bfloat162float(__float2bfloat16_rn(lo)), hi - __bfloat162float(__float2bfloat16_rn(hi)));
+}
 
 struct AttnArgs {
     CUtensorMap map_k, map_v;          // TMA mode: the pools as [pages * kv heads * page size, hd] matrices
@@ -49,6 +53,8 @@ struct AttnArgs {
                                        // query sees when the slope is >= 0)
     const float* sinks;                // per query head, or nullptr: one more softmax slot whose score is this number as it
                                        // stands (not scaled), without key or value; it joins the denominator once
+    int weights_hi_lo;                 // the softmax weights enter P V as two bfloat16 numbers each (the rounded weight and
+                                       // the rounding's remainder): 16 bits of mantissa instead of 8, two MMAs for one
     float* part_o; float* part_ml;     // split-key: partial results, [slot][16 rows][HD_MAX] and [slot][16][2]
     int* part_cnt;                     // split-key: per (sequence, key/value head), segments that have arrived; 0 at rest
     int n_seqs;                        // sequences of the step

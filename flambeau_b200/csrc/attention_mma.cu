@@ -329,6 +329,16 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
         // ---- O += P V: every V fragment serves all R row blocks ----
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
+            uint32_t pl[R][4];     // what rounding left of the weights (s still holds them in float32)
+            if (a.weights_hi_lo) {
+#pragma unroll
+                for (int rb = 0; rb < R; ++rb) {
+                    pl[rb][0] = pack_bf16_remainder(s[rb][2 * kk][0], s[rb][2 * kk][1]);
+                    pl[rb][1] = pack_bf16_remainder(s[rb][2 * kk][2], s[rb][2 * kk][3]);
+                    pl[rb][2] = pack_bf16_remainder(s[rb][2 * kk + 1][0], s[rb][2 * kk + 1][1]);
+                    pl[rb][3] = pack_bf16_remainder(s[rb][2 * kk + 1][2], s[rb][2 * kk + 1][3]);
+                }
+            }
 #pragma unroll
             for (int d = 0; d < NDB; d += 2) {
                 uint32_t b[4];     // (b0,b1): dims d*8..+7, (b2,b3): dims (d+1)*8..+7, keys kk*16..+15
@@ -338,6 +348,10 @@ attention_mma_kernel(const __grid_constant__ AttnArgs a) {
                 for (int rb = 0; rb < R; ++rb) {
                     mma_bf16(o[rb][d], pa[rb][kk], b[0], b[1]);
                     mma_bf16(o[rb][d + 1], pa[rb][kk], b[2], b[3]);
+                    if (a.weights_hi_lo) {
+                        mma_bf16(o[rb][d], pl[rb], b[0], b[1]);
+                        mma_bf16(o[rb][d + 1], pl[rb], b[2], b[3]);
+                    }
                 }
             }
         }
@@ -437,7 +451,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
                                   const int* seq_q_start, const int* seq_q_len, const int* seq_pos_start,
                                   const int* multi_seqs, int n_multi, int n_seqs, int max_q_len, int max_kv_len, int any_short, int any_long, int nh, int nkv, int hd,
                                   int window, float scale, const float* score_slopes, const float* sinks,
-                                  float* scratch,
+                                  int weights_hi_lo, float* scratch,
                                   long long scratch_floats,
                                   const void* prefetch_base, long long prefetch_rows, long long prefetch_row_stride,
                                   int prefetch_bytes_per_row, int* status, cudaStream_t stream) {
@@ -464,6 +478,7 @@ FB_API int fb_paged_attention_mma(const void* q, long long q_stride, void* out, 
     a.scale_log2e = scale * 1.4426950408889634f;
     a.score_slopes = score_slopes;
     a.sinks = sinks;
+    a.weights_hi_lo = weights_hi_lo ? 1 : 0;
     a.status = status;
     a.short_rows = G <= 16 ? 16 : 0;               // with more than 16 heads per group even one token is "long"
     if (a.short_rows == 0) {                       // then single tokens run in the arrangement for portions as well,

@@ -483,12 +483,24 @@ attention_split_kernel(const __grid_constant__ AttnArgs a) {
                 pa[3] = pack_bf16(s[1][2], s[1][3]);
                 // ---- O += P V ----
 #pragma unroll
+                uint32_t pl[4] = {0u, 0u, 0u, 0u};    // what rounding left of the weights
+                if (a.weights_hi_lo) {
+                    pl[0] = pack_bf16_remainder(s[0][0], s[0][1]);
+                    pl[1] = pack_bf16_remainder(s[0][2], s[0][3]);
+                    pl[2] = pack_bf16_remainder(s[1][0], s[1][1]);
+                    pl[3] = pack_bf16_remainder(s[1][2], s[1][3]);
+                }
+#pragma unroll
                 for (int d = 0; d < NDB; d += 2) {
                     uint32_t b[4];     // (b0,b1): dims d*8..+7, (b2,b3): dims (d+1)*8..+7, this warp's 16 keys
                     ldmatrix_x4_trans(b, tile_at<HD_MAX, TMA>(vt, key0 + (lane & 7) + 8 * ((lane >> 3) & 1),
                                                               d * 8 + 8 * (lane >> 4)));
                     mma_bf16(o[d], pa, b[0], b[1]);
                     mma_bf16(o[d + 1], pa, b[2], b[3]);
+                    if (a.weights_hi_lo) {
+                        mma_bf16(o[d], pl, b[0], b[1]);
+                        mma_bf16(o[d + 1], pl, b[2], b[3]);
+                    }
                 }
             }
             __syncwarp();

@@ -71,8 +71,8 @@ _SIGNATURES = {
     "fb_diff_attention_mma": (I, [P, L, P, L, P, P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, F, I,
                                   P, L, P, STREAM]),
     # attention_mma.cu
-    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P, P, L, P,
-                                   L, L, I, P, STREAM]),
+    "fb_paged_attention_mma": (I, [P, L, P, L, P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P, I, P, L,
+                                   P, L, L, I, P, STREAM]),
     # sampling.cu
     "fb_apply_penalties": (I, [P, L, I, P, P, P, P, P, P, I, STREAM]),
     "fb_apply_logit_bias": (I, [P, L, I, P, P, P, I, STREAM]),

@@ -666,7 +666,8 @@ def mma_attention_supported(q: torch.Tensor, nh: int, nkv: int, hd: int) -> bool
 def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, n_seqs: int,
                         max_q_len: int, max_kv_len: int, any_short: bool, any_long: bool, nh: int, nkv: int,
                         hd: int, window: int, scale: float, status, table_base=None, prefetch=None,
-                        multi_seqs=None, n_multi: int = 0, score_slopes=None, sinks=None) -> None:
+                        multi_seqs=None, n_multi: int = 0, score_slopes=None, sinks=None,
+                        weights_float32: bool = False) -> None:
     """bfloat16 attention on the tensor cores over the paged cache; sequences are described per entry of the
     step (first row, rows, first position).  any_short / any_long say whether the step holds sequences with
     rows * (nh/nkv) <= 16 / > 16, which run in different arrangements of the kernel.  table_base (int32 per
@@ -675,7 +676,10 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
     n_multi sequences of the step that bring more than one token; the kernels for portions then lay their grid over
     these instead of over every sequence.  score_slopes (float32 per query head, optional): slope * (key position -
     query position) is added to every scaled score; portions then run on the mma.sync kernel.  sinks (float32 per
-    query head, optional): one more softmax slot per head, its score that number unscaled, without key or value."""
+    query head, optional): one more softmax slot per head, its score that number unscaled, without key or value.
+    weights_float32: the softmax weights enter P V as two bfloat16 numbers each (the rounded weight and what the
+    rounding left: 16 bits of mantissa, two MMAs for one) instead of rounded to bfloat16; portions then run on the
+    mma.sync kernel, whose weights are in registers."""
     _cuda(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_len, seq_pos_start, status, table_base, multi_seqs,
           sinks)
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != nh or not sinks.is_contiguous()):
@@ -696,12 +700,12 @@ def paged_attention_mma(q, out, k_pool, v_pool, block_table, seq_q_start, seq_q_
         seq_q_len.data_ptr(), seq_pos_start.data_ptr(), _ptr(multi_seqs), int(n_multi), n_seqs, max_q_len, max_kv_len,
         1 if any_short else 0,
         1 if any_long else 0, nh, nkv, hd, int(window), float(scale), _slopes(score_slopes, nh), _ptr(sinks),
-        scratch.data_ptr(), scratch.numel(),
+        1 if weights_float32 else 0, scratch.data_ptr(), scratch.numel(),
         *prefetch_arguments(prefetch), status.data_ptr(), _stream()), "paged_attention_mma")
 
 
 def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int, scale: float,
-                    next_weight=None, score_slopes=None, sinks=None, vd: int = 0) -> None:
+                    next_weight=None, score_slopes=None, sinks=None, vd: int = 0, weights_float32: bool = False) -> None:
     """Attention of every row of the step over its request's cached keys: the tensor-core kernel for bfloat16
     and head sizes it takes, the float32 CUDA-core kernel otherwise (all of the 32-bit mode).  next_weight: the
     matrix of the product that follows, whose start the bfloat16 kernel may fetch into L2 (a hint)."""
@@ -714,7 +718,7 @@ def paged_attention(ctx, q, out, cache, nh: int, nkv: int, hd: int, window: int,
                             b.seq_pos_start_d, b.n_seqs, b.max_q_len, b.max_kv_len, any(short), not all(short),
                             nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,
                             prefetch=next_weight, multi_seqs=b.multi_seqs_d, n_multi=b.n_multi,
-                            score_slopes=score_slopes, sinks=sinks)
+                            score_slopes=score_slopes, sinks=sinks, weights_float32=weights_float32)
     else:
         paged_attention_simt(q, out, cache.k_pool, cache.v_pool, cache.block_table, b.positions, b.row_seq,
                              nh, nkv, hd, window, scale, ctx.runtime.status, table_base=cache.table_base,

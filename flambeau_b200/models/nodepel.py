@@ -34,7 +34,7 @@ def build_spec(cfg: NodepelConfig) -> ModelSpec:
         a, r = layer.mixer.left, layer.mixer.right
         left = PartSpec("mixer", "attention", dict(
             width=D, num_heads=a.heads, num_kv_heads=a.kv_heads, head_dim=a.dim, value_dim=a.vdim, window=a.window,
-            scale=a.scale, sink=True, names=LEFT_NAMES, qk_norm_reach="projection",
+            scale=a.scale, sink=True, names=LEFT_NAMES, qk_norm_reach="projection", weights_float32=True,
             qk_norm=PartSpec("norm", "rmsnorm", dict(width=a.dim, eps=cfg.norm_eps, init=("one_plus_normal", 0.1))),
             position=PartSpec("position", "rotary_half", dict(head_dim=a.dim, theta=a.rot_base, rotary_dim=a.rot_dims))
             if a.rot_dims else None), p + "mix.left.")

@@ -37,6 +37,10 @@ class PagedAttention(Mixer):
     num_heads * value_dim columns.
     `sink` (bool): the softmax of every head has one more slot, a learned score per head (`<prefix><names.sink>`,
     [num_heads]) that is not scaled, has no key and no value, and counts once in the denominator.
+    `weights_float32`: the softmax weights keep 16 bits of mantissa through the product with the values when serving
+    in bfloat16 (two bfloat16 numbers a weight, two MMAs for one; the 32-bit mode has them in float32 anyway), for
+    designs that say their attention weights are 32-bit numbers; otherwise they are rounded to bfloat16 for that
+    product, as flash attention kernels do.
     `names`: what the tensors are called behind the prefix (keys q, k, v, o, q_norm, k_norm, sink), for checkpoints
     with other names than the defaults."""
     graph_safe = True
@@ -47,11 +51,13 @@ class PagedAttention(Mixer):
     def __init__(self, runtime=None, prefix="", *, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  window: int = 0, position: PartSpec | None = None, scale: float | None = None,
                  init_std: float = 0.02, qk_norm: PartSpec | None = None, distance_slopes=None,
-                 qk_norm_reach: str = "head", value_dim: int | None = None, sink: bool = False, names=None):
+                 qk_norm_reach: str = "head", value_dim: int | None = None, sink: bool = False, names=None,
+                 weights_float32: bool = False):
         super().__init__(runtime, prefix)
         self.width, self.nh, self.nkv, self.hd = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
         self.vd = int(value_dim) if value_dim else self.hd
         self.sink = bool(sink)
+        self.weights_float32 = bool(weights_float32)
         self.names = dict(self.DEFAULT_NAMES)
         self.names.update(names or {})
         if qk_norm_reach not in ("head", "projection"):
@@ -158,7 +164,8 @@ class PagedAttention(Mixer):
                 a = ctx.ws.alloc((n, self.nh * self.vd), rt.dtype)
                 hint = self.o.weight if ctx.l2_hints and n <= 64 else None
                 ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
-                                    next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks, vd=self.vd)
+                                    next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks, vd=self.vd,
+                                    weights_float32=self.weights_float32)
                 ctx.to_stream(self.o, a)
                 return
             if self.vd != self.hd or self.qk_norm_reach != "head":
@@ -203,7 +210,8 @@ class PagedAttention(Mixer):
             # few rows: the attention kernel fetches the start of the output projection's weights into L2 at its end
             hint = self.o.weight if ctx.l2_hints and n <= 64 else None
             ops.paged_attention(ctx, q, a, cache, self.nh, self.nkv, self.hd, self.window, self.scale,
-                                next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks)
+                                next_weight=hint, score_slopes=self.distance_slopes, sinks=self.sinks,
+                                weights_float32=self.weights_float32)
             ctx.to_stream(self.o, a)
 
 

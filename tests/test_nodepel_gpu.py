@@ -125,10 +125,15 @@ def test_windowed_attention_with_a_sink(geometry, dtype):
         assert ops.mma_attention_supported(q_d, nh, nkv, hd)
         G = nh // nkv
         starts = [sum(lens[:i]) for i in range(len(lens))]
-        ops.paged_attention_mma(q_d, out, c.k_pool, c.v_pool, c.block_table, i32(starts), i32(lens),
-                                i32([ctx for ctx, _ in seqs]), len(seqs), max(lens), max(ctx + n for ctx, n in seqs),
-                                any(n * G <= 16 for n in lens), any(n * G > 16 for n in lens), nh, nkv, hd, window,
-                                scale, status, table_base=c.table_base, sinks=sink.float().to(DEV))
+        args = (c.k_pool, c.v_pool, c.block_table, i32(starts), i32(lens), i32([ctx for ctx, _ in seqs]), len(seqs),
+                max(lens), max(ctx + n for ctx, n in seqs), any(n * G <= 16 for n in lens),
+                any(n * G > 16 for n in lens), nh, nkv, hd, window, scale, status)
+        # the weights as two bfloat16 numbers each through P V: what is left is the rounding of the output
+        exact = torch.empty_like(out)
+        ops.paged_attention_mma(q_d, exact, *args, table_base=c.table_base, sinks=sink.float().to(DEV),
+                                weights_float32=True)
+        assert rel_err(exact, want) < 5e-3
+        ops.paged_attention_mma(q_d, out, *args, table_base=c.table_base, sinks=sink.float().to(DEV))
     else:
         ops.paged_attention_simt(q_d, out, c.k_pool, c.v_pool, c.block_table, pos,
                                  i32([s for s, n in enumerate(lens) for _ in range(n)]), nh, nkv, hd, window, scale,
